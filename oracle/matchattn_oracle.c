@@ -1,0 +1,322 @@
+/*
+ * CPU oracle for the MatchAttention operator.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is a plain-C restatement of the algorithm of the reference's
+ * 'pytorch' MatchAttention path.  It exists so that the CUDA kernels can be
+ * checked against it and so that the benchmark can time a CPU baseline; it is
+ * never linked into, imported by or called from the shipped library.
+ *
+ * Parity status: pinned.  The restatement is compared, in the CPU test suite,
+ * with golden vectors produced by executing the reference's own Python
+ * functions (models/mat_pytorch_impl.py) on seeded inputs; the script that
+ * made the vectors is tests/golden/make_golden.py.
+ *
+ * What is restated (reference file:line):
+ *   - window origin  floor(max_offset)            models/attention_blocks.py:82
+ *   - bilinear weights [nw, ne, sw, se]           models/mat_pytorch_impl.py:3-27
+ *   - tap grid, replicate-border index clamp,
+ *     negative L1 score                            models/mat_pytorch_impl.py:29-76
+ *   - score * scale                                models/attention_blocks.py:86
+ *   - BilinearSoftmax: four shifted (2r+1)^2
+ *     sub-windows, one softmax each, weighted,
+ *     summed back in the order nw, ne, sw, se      models/mat_pytorch_impl.py:78-165
+ *   - weighted sum of the gathered values          models/mat_pytorch_impl.py:167-178
+ *
+ * Rounding model for the 16-bit types.  Eager PyTorch evaluates each
+ * elementwise op in fp32 and rounds the result to the tensor dtype, and it
+ * accumulates reductions (sum, softmax) in fp32 and rounds once.  RND() below
+ * marks every place where such a rounding happens; for fp32 it is the
+ * identity.
+ *
+ * Layout (all arrays contiguous, row-major):
+ *   max_offset [B, Nq, h, 2]   absolute (x, y) sampling centre in token units
+ *   q          [B, Nq, h*hd]
+ *   k, v       [B, H*W, h*hd]
+ *   out        [B, Nq, h*hd]
+ *   attn_out   [B, Nq, h, (2r+2)^2]      (may be NULL)
+ * with Nq = (q_row_end - q_row_begin) * W: the query arrays hold only the rows
+ * of the band, keys and values always hold the whole map.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <pthread.h>
+#include <unistd.h>
+
+#define MA_MAX_R 4
+#define MA_MAX_TAPS ((2 * MA_MAX_R + 2) * (2 * MA_MAX_R + 2))
+
+enum { MA_F32 = 0, MA_F16 = 1, MA_BF16 = 2 };
+
+/* ---- 16-bit float conversions, written out so that the result does not
+ * depend on compiler flags or on F16C being present ---------------------- */
+
+static inline uint32_t f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+static float g_half_table[65536];
+static int g_half_table_ready = 0;
+
+static float half_bits_to_float_slow(uint16_t hbits)
+{
+    uint32_t sign = (uint32_t)(hbits & 0x8000u) << 16;
+    uint32_t expo = (hbits >> 10) & 0x1fu;
+    uint32_t mant = hbits & 0x3ffu;
+    if (expo == 0x1fu) return u2f(sign | 0x7f800000u | (mant << 13));
+    if (expo == 0) {
+        /* zero or subnormal: value = mant * 2^-24, exact in fp32 */
+        float mag = (float)mant * (1.0f / 16777216.0f);
+        return sign ? -mag : mag;
+    }
+    return u2f(sign | ((expo + 112u) << 23) | (mant << 13));
+}
+
+static void ensure_half_table(void)
+{
+    if (g_half_table_ready) return;
+    for (uint32_t i = 0; i < 65536u; ++i) g_half_table[i] = half_bits_to_float_slow((uint16_t)i);
+    g_half_table_ready = 1;
+}
+
+/* fp32 -> fp16 bits, round to nearest even, with subnormals, inf and nan */
+static inline uint16_t float_to_half_bits(float f)
+{
+    uint32_t u = f2u(f);
+    uint32_t sign = (u >> 16) & 0x8000u;
+    uint32_t au = u & 0x7fffffffu;
+    if (au >= 0x7f800000u) /* inf or nan */
+        return (uint16_t)(sign | 0x7c00u | ((au > 0x7f800000u) ? 0x200u : 0u));
+    if (au >= 0x477ff000u) /* rounds to or beyond 65520 -> inf */
+        return (uint16_t)(sign | 0x7c00u);
+    if (au < 0x38800000u) { /* below 2^-14: subnormal half (or zero) */
+        /* adding 0.5 (fp32) aligns the value so that the low mantissa bits
+         * are the subnormal half, already rounded to nearest even */
+        float shifted = u2f(au) + 0.5f;
+        return (uint16_t)(sign | (f2u(shifted) - 0x3f000000u));
+    }
+    uint32_t lsb = (au >> 13) & 1u;
+    au += 0xfffu + lsb;              /* round to nearest even on bit 13 */
+    return (uint16_t)(sign | ((au - 0x38000000u) >> 13));
+}
+
+static inline float bf16_bits_to_float(uint16_t b) { return u2f((uint32_t)b << 16); }
+
+static inline uint16_t float_to_bf16_bits(float f)
+{
+    uint32_t u = f2u(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+static inline float load_elem(const void *p, int64_t i, const int dt)
+{
+    if (dt == MA_F32) return ((const float *)p)[i];
+    if (dt == MA_F16) return g_half_table[((const uint16_t *)p)[i]];
+    return bf16_bits_to_float(((const uint16_t *)p)[i]);
+}
+
+static inline void store_elem(void *p, int64_t i, float val, const int dt)
+{
+    if (dt == MA_F32) ((float *)p)[i] = val;
+    else if (dt == MA_F16) ((uint16_t *)p)[i] = float_to_half_bits(val);
+    else ((uint16_t *)p)[i] = float_to_bf16_bits(val);
+}
+
+/* round an fp32 value to the tensor dtype and return it as fp32 */
+static inline float rnd(float val, const int dt)
+{
+    if (dt == MA_F32) return val;
+    if (dt == MA_F16) return g_half_table[float_to_half_bits(val)];
+    return bf16_bits_to_float(float_to_bf16_bits(val));
+}
+#define RND(v) rnd((v), dt)
+
+/* floor of a coordinate, limited to the range in which the replicate clamp
+ * of the taps still gives the same answer; keeps the int conversion defined */
+static inline int origin_of(float coord, int r, int extent)
+{
+    float fl = floorf(coord);
+    float lo = (float)(-(r + 2)), hi = (float)(extent + r + 1);
+    if (!(fl >= lo)) fl = lo;
+    if (fl > hi) fl = hi;
+    return (int)fl;
+}
+
+static inline int clampi(int a, int lo, int hi) { return a < lo ? lo : (a > hi ? hi : a); }
+
+/* One (query, head): everything from the window origin to the output slice.
+ * always_inline + a literal dt at the call sites gives one specialised copy
+ * per dtype. */
+static inline __attribute__((always_inline)) void
+one_query_head(const void *mo, const void *q, const void *k, const void *v, void *out, void *attn_out,
+               int64_t bq /* b*Nq + nq */, int64_t kbase /* b*H*W */, int head,
+               int H, int W, int h, int hd, int r, float scale, const int dt)
+{
+    const int side = 2 * r + 2, sub = 2 * r + 1, M = side * side;
+    const int C = h * hd;
+    const int64_t lh = bq * h + head;
+
+    /* models/mat_pytorch_impl.py:11-25 */
+    const float x = load_elem(mo, lh * 2, dt), y = load_elem(mo, lh * 2 + 1, dt);
+    const float dx = RND(x - floorf(x)), dy = RND(y - floorf(y));
+    const float ex = RND(1.0f - dx), ey = RND(1.0f - dy);
+    const float wgt[4] = { RND(ex * ey), RND(dx * ey), RND(ex * dy), RND(dx * dy) };
+
+    /* models/attention_blocks.py:82 and models/mat_pytorch_impl.py:45-61 */
+    const int x0 = origin_of(x, r, W), y0 = origin_of(y, r, H);
+    int64_t tap_tok[MA_MAX_TAPS];
+    for (int j = 0; j < side; ++j) {
+        const int ty = clampi(y0 - r + j, 0, H - 1);
+        for (int i = 0; i < side; ++i) {
+            const int tx = clampi(x0 - r + i, 0, W - 1);
+            tap_tok[j * side + i] = kbase + (int64_t)ty * W + tx;
+        }
+    }
+
+    /* models/mat_pytorch_impl.py:74 then models/attention_blocks.py:86 */
+    float score[MA_MAX_TAPS];
+    const int64_t qoff = bq * C + (int64_t)head * hd;
+    for (int m = 0; m < M; ++m) {
+        const int64_t koff = tap_tok[m] * C + (int64_t)head * hd;
+        float acc = 0.0f;
+        for (int c = 0; c < hd; ++c)
+            acc += fabsf(RND(load_elem(q, qoff + c, dt) - load_elem(k, koff + c, dt)));
+        score[m] = RND(RND(-RND(acc)) * scale);
+    }
+
+    /* models/mat_pytorch_impl.py:148-165: sub-window t is shifted by
+     * (row t/2, column t%2); softmax, weight, then accumulate in place */
+    float a[MA_MAX_TAPS];
+    for (int m = 0; m < M; ++m) a[m] = 0.0f;
+    for (int t = 0; t < 4; ++t) {
+        const int oy = t >> 1, ox = t & 1;
+        float mx = -INFINITY;
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) {
+                const float s = score[(j + oy) * side + i + ox];
+                mx = s > mx ? s : mx;
+            }
+        float e[(2 * MA_MAX_R + 1) * (2 * MA_MAX_R + 1)];
+        float den = 0.0f;
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) {
+                const float ev = expf(score[(j + oy) * side + i + ox] - mx);
+                e[j * sub + i] = ev;
+                den += ev;
+            }
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) {
+                const int m = (j + oy) * side + i + ox;
+                const float p = RND(e[j * sub + i] / den);
+                a[m] = RND(a[m] + RND(wgt[t] * p));
+            }
+    }
+    if (attn_out)
+        for (int m = 0; m < M; ++m) store_elem(attn_out, lh * M + m, a[m], dt);
+
+    /* models/mat_pytorch_impl.py:176 */
+    for (int c = 0; c < hd; ++c) {
+        float acc = 0.0f;
+        for (int m = 0; m < M; ++m)
+            acc += RND(a[m] * load_elem(v, tap_tok[m] * C + (int64_t)head * hd + c, dt));
+        store_elem(out, qoff + c, acc, dt);
+    }
+}
+
+const char *matchattn_oracle_strerror(int code)
+{
+    switch (code) {
+    case 0: return "ok";
+    case 1: return "null pointer";
+    case 2: return "bad shape";
+    case 3: return "window does not fit the token map";
+    case 4: return "unsupported dtype";
+    case 5: return "window radius too large for the oracle";
+    default: return "unknown";
+    }
+}
+
+/* Work of one thread: a contiguous range of (batch, query) indices. */
+typedef struct {
+    const void *mo, *q, *k, *v;
+    void *out, *attn_out;
+    int64_t first, last, Nq, N;
+    int H, W, h, hd, r, dtype;
+    float scale;
+} ma_job;
+
+static void *run_job(void *arg)
+{
+    const ma_job *jb = (const ma_job *)arg;
+    for (int64_t bq = jb->first; bq < jb->last; ++bq) {
+        const int64_t kbase = (bq / jb->Nq) * jb->N;
+        for (int head = 0; head < jb->h; ++head) {
+            switch (jb->dtype) {
+            case MA_F32:
+                one_query_head(jb->mo, jb->q, jb->k, jb->v, jb->out, jb->attn_out, bq, kbase, head,
+                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_F32);
+                break;
+            case MA_F16:
+                one_query_head(jb->mo, jb->q, jb->k, jb->v, jb->out, jb->attn_out, bq, kbase, head,
+                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_F16);
+                break;
+            default:
+                one_query_head(jb->mo, jb->q, jb->k, jb->v, jb->out, jb->attn_out, bq, kbase, head,
+                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_BF16);
+                break;
+            }
+        }
+    }
+    return NULL;
+}
+
+int matchattn_oracle_max_threads(void)
+{
+    long n = sysconf(_SC_NPROCESSORS_ONLN);
+    return n > 0 ? (int)n : 1;
+}
+
+/* Returns 0 on success.  nthreads <= 0 means "all online cores". */
+int matchattn_oracle_forward(const void *max_offset, const void *q, const void *k, const void *v,
+                             void *out, void *attn_out,
+                             int B, int H, int W, int h, int hd, int r, int dtype, float scale,
+                             int q_row_begin, int q_row_end, int nthreads)
+{
+    if (!max_offset || !q || !k || !v || !out) return 1;
+    if (B <= 0 || H <= 0 || W <= 0 || h <= 0 || hd <= 0 || r < 0) return 2;
+    if (q_row_begin < 0 || q_row_end > H || q_row_begin >= q_row_end) return 2;
+    if (2 * r + 2 > H || 2 * r + 2 > W) return 3; /* models/attention_blocks.py:64 */
+    if (dtype != MA_F32 && dtype != MA_F16 && dtype != MA_BF16) return 4;
+    if (r > MA_MAX_R) return 5;
+    ensure_half_table();
+
+    const int64_t Nq = (int64_t)(q_row_end - q_row_begin) * W;
+    const int64_t total = (int64_t)B * Nq;
+    if (nthreads <= 0) nthreads = matchattn_oracle_max_threads();
+    if (nthreads > 256) nthreads = 256;
+    if ((int64_t)nthreads > total) nthreads = (int)total;
+
+    ma_job jobs[256];
+    pthread_t tids[256];
+    for (int t = 0; t < nthreads; ++t) {
+        ma_job *jb = &jobs[t];
+        jb->mo = max_offset; jb->q = q; jb->k = k; jb->v = v; jb->out = out; jb->attn_out = attn_out;
+        jb->first = total * t / nthreads;
+        jb->last = total * (t + 1) / nthreads;
+        jb->Nq = Nq; jb->N = (int64_t)H * W;
+        jb->H = H; jb->W = W; jb->h = h; jb->hd = hd; jb->r = r; jb->dtype = dtype; jb->scale = scale;
+    }
+    int started = 0;
+    for (int t = 1; t < nthreads; ++t) {
+        if (pthread_create(&tids[t], NULL, run_job, &jobs[t]) != 0) break;
+        started = t;
+    }
+    run_job(&jobs[0]);
+    /* a thread that could not be started has its range done here */
+    for (int t = started + 1; t < nthreads; ++t) run_job(&jobs[t]);
+    for (int t = 1; t <= started; ++t) pthread_join(tids[t], NULL);
+    return 0;
+}

@@ -1,0 +1,114 @@
+"""Shared helpers for the tests: golden-file loading, seeded workload
+generators and the tolerance rules."""
+from __future__ import annotations
+
+import glob
+import os
+
+import numpy as np
+import torch
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+DTYPES = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+
+# Tolerances.  float32: 1e-4 relative (|err| <= 1e-4 * max(|ref|, 1)).
+# float16: 2e-3 absolute.  bfloat16 has 8 significand bits against float16's 11,
+# so its bound is 8x the float16 one.
+ABS_TOL = {torch.float16: 2e-3, torch.bfloat16: 1.6e-2}
+REL_TOL_F32 = 1e-4
+
+
+def golden_names(pattern="*"):
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, pattern + ".npz")))
+
+
+def load_golden(name):
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    dt = DTYPES[str(z["dtype"])]
+
+    def t(key):
+        a = torch.from_numpy(z[key].copy())
+        return a.view(torch.bfloat16) if dt == torch.bfloat16 else a
+
+    return dict(dtype=dt, H=int(z["H"]), W=int(z["W"]), h=int(z["h"]), r=int(z["r"]), scale=float(z["scale"]),
+                max_offset=t("max_offset"), q=t("q"), k=t("k"), v=t("v"), out=t("out"), attn=t("attn"))
+
+
+def excess(got, ref, dtype):
+    """max over elements of |got-ref| / allowed; <= 1 passes."""
+    g, r = got.detach().cpu().float(), ref.detach().cpu().float()
+    if not torch.isfinite(g).all():
+        return float("inf")
+    err = (g - r).abs()
+    if dtype == torch.float32:
+        allowed = REL_TOL_F32 * r.abs().clamp_min(1.0)
+    else:
+        allowed = torch.full_like(err, ABS_TOL[dtype])
+    return float((err / allowed).max()) if err.numel() else 0.0
+
+
+def assert_close(got, ref, dtype, what=""):
+    e = excess(got, ref, dtype)
+    assert e <= 1.0, f"{what}: error is {e:.3f}x the allowed tolerance for {dtype}"
+
+
+def grid_xy(B, H, W, h, rows=None):
+    r0, r1 = (0, H) if rows is None else rows
+    ys, xs = torch.meshgrid(torch.arange(r0, r1, dtype=torch.float32), torch.arange(W, dtype=torch.float32),
+                            indexing="ij")
+    return torch.stack((xs, ys), dim=-1).view(1, (r1 - r0) * W, 1, 2).repeat(B, 1, h, 1)
+
+
+def clamp_like_caller(mo, H, W, r):
+    """What the caller does before the op: clamp in the tensor dtype, with the
+    upper bound itself rounded to that dtype (so W-1-r-1e-3 becomes W-1-r in
+    float16)."""
+    dt = mo.dtype
+    lo = torch.tensor(float(r), dtype=dt)
+    hx = torch.tensor(W - 1 - r - 1e-3, dtype=dt)
+    hy = torch.tensor(H - 1 - r - 1e-3, dtype=dt)
+    x = torch.clamp(mo[..., 0:1], min=lo, max=hx)
+    y = torch.clamp(mo[..., 1:2], min=lo, max=hy)
+    return torch.cat((x, y), dim=-1).contiguous()
+
+
+def make_inputs(seed, B, H, W, h, hd, r, dtype, kind="flow", spread=24.0, border_frac=0.1, per_head=False):
+    """Seeded synthetic op inputs.
+
+    kind 'flow'  : x,y offsets uniform in [-spread, spread] tokens, `border_frac` of the queries get a
+                   centre within r+1 tokens of (or beyond) an edge and are left unclamped, the rest are
+                   clamped the way the caller clamps them.
+    kind 'cross' : x uniform in [-spread, 0], y = 0, same for all heads, clamped.
+    kind 'self'  : x,y uniform in [-3, 3] per head, clamped.
+    kind 'raw'   : centres anywhere up to 0.75 map sizes away, never clamped.
+    """
+    g = torch.Generator().manual_seed(seed)
+    N, C = H * W, h * hd
+    q, k, v = (torch.randn(B, N, C, generator=g).to(dtype) for _ in range(3))
+    grid = grid_xy(B, H, W, h)
+    hh = h if per_head else 1
+    if kind == "flow":
+        rel = torch.empty(B, N, hh, 2).uniform_(-spread, spread, generator=g).expand(B, N, h, 2)
+        mo = clamp_like_caller((grid + rel).to(dtype), H, W, r)
+        pick = torch.rand(B, N, 1, 1, generator=g) < border_frac
+        edge = torch.randint(0, 4, (B, N, 1, 1), generator=g)
+        depth = torch.empty(B, N, hh, 1).uniform_(-(r + 1.0), r + 1.0, generator=g).expand(B, N, h, 1)
+        along = torch.rand(B, N, hh, 1, generator=g).expand(B, N, h, 1)
+        bx = torch.where(edge == 0, depth, torch.where(edge == 1, (W - 1) - depth, along * (W - 1)))
+        by = torch.where(edge == 2, depth, torch.where(edge == 3, (H - 1) - depth, along * (H - 1)))
+        bx = torch.where(edge >= 2, along * (W - 1), bx)
+        by = torch.where(edge < 2, along * (H - 1), by)
+        border = torch.cat((bx, by), dim=-1).to(dtype)
+        mo = torch.where(pick, border, mo).contiguous()
+    elif kind == "cross":
+        rx = torch.empty(B, N, 1, 1).uniform_(-spread, 0.0, generator=g).expand(B, N, h, 1)
+        mo = clamp_like_caller((grid + torch.cat((rx, torch.zeros_like(rx)), -1)).to(dtype), H, W, r)
+    elif kind == "self":
+        rel = torch.empty(B, N, h, 2).uniform_(-3.0, 3.0, generator=g)
+        mo = clamp_like_caller((grid + rel).to(dtype), H, W, r)
+    elif kind == "raw":
+        rel = torch.empty(B, N, hh, 2).uniform_(-1.0, 1.0, generator=g).expand(B, N, h, 2)
+        mo = (grid + rel * torch.tensor([W * 0.75, H * 0.75])).to(dtype).contiguous()
+    else:
+        raise ValueError(kind)
+    return mo, q, k, v

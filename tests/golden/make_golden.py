@@ -1,0 +1,212 @@
+"""Generate the golden vectors under tests/golden/ by RUNNING THE REFERENCE.
+
+Usage (only where the reference checkout exists; it is imported, not copied):
+
+    python tests/golden/make_golden.py [--ref /path/to/MatchAttention]
+
+Each .npz holds seeded inputs and the outputs of the reference's own functions
+(models/mat_pytorch_impl.py, driven exactly as models/attention_blocks.py:79-91
+drives them) on those inputs.  bfloat16 arrays are stored as their int16 bit
+patterns (numpy has no bfloat16); the key ``dtype`` says how to read them.
+
+The files are derived artefacts: the tests compare the CPU oracle and the CUDA
+kernels with them, so that parity is checked even where the reference is not
+installed.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def install_timm_shim():
+    """The reference imports four helpers from timm, which is not installed."""
+    if "timm" in sys.modules:
+        return
+    import torch.nn as nn
+
+    class DropPath(nn.Module):
+        def __init__(self, p=0.0):
+            super().__init__()
+
+        def forward(self, x):
+            return x
+
+    def to_2tuple(x):
+        return tuple(x) if isinstance(x, (tuple, list)) else (x, x)
+
+    def register_model(fn):
+        return fn
+
+    pkgs = {n: types.ModuleType(n) for n in (
+        "timm", "timm.models", "timm.models.layers", "timm.models.layers.helpers", "timm.models.registry")}
+    pkgs["timm.models.layers"].DropPath = DropPath
+    pkgs["timm.models.layers"].trunc_normal_ = torch.nn.init.trunc_normal_
+    pkgs["timm.models.layers.helpers"].to_2tuple = to_2tuple
+    pkgs["timm.models.registry"].register_model = register_model
+    pkgs["timm"].models = pkgs["timm.models"]
+    pkgs["timm.models"].layers = pkgs["timm.models.layers"]
+    pkgs["timm.models"].registry = pkgs["timm.models.registry"]
+    pkgs["timm.models.layers"].helpers = pkgs["timm.models.layers.helpers"]
+    sys.modules.update(pkgs)
+
+
+def import_reference(ref_root):
+    install_timm_shim()
+    sys.path.insert(0, ref_root)
+    import models.mat_pytorch_impl as impl
+    import models.attention_blocks as blocks
+    return impl, blocks
+
+
+def reference_op(impl, max_offset, q, k, v, H, W, h, r, scale):
+    """The 'pytorch' branch of MatchAttention.forward (attention_blocks.py:82-91), no dropout."""
+    B, N, _ = q.shape
+    win_r = [r, r]
+    m_id = torch.floor(max_offset).to(torch.int32)
+    wgt = impl.compute_bilinear_weights(max_offset)
+    attn, idx = impl.compute_match_attention(q.view(B, N, h, -1), k.view(B, N, h, -1), m_id, win_r, H, W)
+    attn = attn * scale
+    attn = impl.compute_bilinear_softmax(attn, wgt, win_r)
+    out = impl.attention_aggregate(v.view(B, N, h, -1), attn, idx, win_r)
+    return out, attn
+
+
+def reference_clamp(blocks, max_offset, H, W, r):
+    fake_self = types.SimpleNamespace(win_r=[r, r])
+    return blocks.MatchAttention.clamp_max_offset(fake_self, max_offset, H, W)
+
+
+def grid_xy(B, H, W, h):
+    ys, xs = torch.meshgrid(torch.arange(H, dtype=torch.float32), torch.arange(W, dtype=torch.float32), indexing="ij")
+    g = torch.stack((xs, ys), dim=-1).view(1, H * W, 1, 2)
+    return g.repeat(B, 1, h, 1)
+
+
+def to_np(t):
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy()
+    return t.numpy()
+
+
+def save_case(name, dtype, H, W, h, r, scale, mo, q, k, v, out, attn, note):
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(
+        path, dtype=str(dtype).replace("torch.", ""), H=H, W=W, h=h, r=r, scale=np.float64(scale),
+        max_offset=to_np(mo), q=to_np(q), k=to_np(k), v=to_np(v), out=to_np(out), attn=to_np(attn), note=note)
+    print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
+def synthetic_cases(impl, blocks):
+    specs = [
+        # name, seed, B, H, W, h, hd, r, kind
+        ("raw_r1", 11, 2, 6, 7, 2, 8, 1, "raw"),
+        ("raw_r2", 12, 1, 7, 9, 3, 8, 2, "raw"),
+        ("cross_r1", 13, 1, 13, 26, 8, 16, 1, "cross"),
+        ("self_r1", 14, 1, 13, 26, 8, 16, 1, "self"),
+        ("model_r2_hd40", 15, 2, 8, 10, 4, 40, 2, "self"),
+        ("model_r1_hd32", 16, 2, 9, 12, 4, 32, 1, "cross"),
+    ]
+    for name, seed, B, H, W, h, hd, r, kind in specs:
+        gen = torch.Generator().manual_seed(seed)
+        N, C = H * W, h * hd
+        q32, k32, v32 = (torch.randn(B, N, C, generator=gen) for _ in range(3))
+        grid = grid_xy(B, H, W, h)
+        if kind == "raw":          # centres anywhere, also outside the map; never clamped
+            rel = torch.empty(B, N, h, 2).uniform_(-1.0, 1.0, generator=gen)
+            rel = rel * torch.tensor([W * 0.75, H * 0.75])
+            mo32 = grid + rel
+            integral = torch.rand(B, N, h, 1, generator=gen) < 0.15   # some exactly integral centres
+            mo32 = torch.where(integral, torch.round(mo32), mo32)
+        elif kind == "cross":      # disparity-like, the same for every head (attention_blocks.py:162)
+            rel_x = torch.empty(B, N, 1, 1).uniform_(-16.0, 0.0, generator=gen).repeat(1, 1, h, 1)
+            mo32 = grid + torch.cat((rel_x, torch.zeros_like(rel_x)), dim=-1)
+        else:                      # per-head small offsets
+            mo32 = grid + torch.empty(B, N, h, 2).uniform_(-3.0, 3.0, generator=gen)
+        scale = hd ** -0.5
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            mo = mo32.to(dtype)
+            if kind != "raw":
+                mo = reference_clamp(blocks, mo, H, W, r)
+            q, k, v = q32.to(dtype), k32.to(dtype), v32.to(dtype)
+            out, attn = reference_op(impl, mo, q, k, v, H, W, h, r, scale)
+            tag = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[dtype]
+            save_case(f"{name}_{tag}", dtype, H, W, h, r, scale, mo, q, k, v, out, attn,
+                      f"seed {seed}, kind {kind}, reference mat_pytorch_impl on CPU")
+
+
+def model_cases(ref_root, impl):
+    """Inputs captured from MatchAttention calls inside a MatchStereo-tiny forward
+    (random-init weights, seeded noise images), one self and one cross call per
+    stage; batch item 0 only, cast to float16; expected = reference op in float16."""
+    from models.match_stereo import MatchStereo
+    from models.attention_blocks import MatchAttention
+    torch.manual_seed(21)
+    args = types.SimpleNamespace(variant="tiny", mat_impl="pytorch")
+    model = MatchStereo(args).eval()
+    captured = []
+
+    def hook(mod, inputs):
+        x, max_offset = inputs[0], inputs[1]
+        B, H, W, _ = x.shape
+        N = H * W
+        xx = x.view(B, N, -1)
+        if mod.cross:
+            a, b = xx.chunk(2, dim=0)
+            ref, tgt = torch.cat((a, b), 0), torch.cat((b, a), 0)
+        else:
+            if mod.noc_embed:
+                xx = torch.cat((xx, inputs[2].view(B, N, -1)), dim=-1)
+            ref, tgt = xx, xx
+        q, k, v = mod.q(ref), mod.k(tgt), mod.v(tgt)
+        mo = mod.clamp_max_offset(max_offset, H, W)
+        captured.append(dict(cross=mod.cross, H=H, W=W, h=mod.num_head, r=mod.win_r[0], scale=mod.scale,
+                             mo=mo.detach(), q=q.detach(), k=k.detach(), v=v.detach()))
+
+    for m in model.modules():
+        if isinstance(m, MatchAttention):
+            m.register_forward_pre_hook(hook)
+    img0 = torch.rand(1, 3, 192, 192) * 255
+    img1 = torch.roll(img0, shifts=-5, dims=-1) + torch.randn(1, 3, 192, 192) * 2
+    with torch.inference_mode():
+        model(img0, img1, stereo=True)
+    print(f"captured {len(captured)} MatchAttention calls")
+    seen = set()
+    for idx, c in enumerate(captured):
+        key = (c["H"], c["cross"])
+        if key in seen:
+            continue
+        # take the LAST layer of each stage instead of the first: fields have moved by then
+        last = max(i for i, d in enumerate(captured) if (d["H"], d["cross"]) == key)
+        c = captured[last]
+        seen.add(key)
+        sl = slice(0, 1)
+        mo, q, k, v = (c[n][sl].to(torch.float16).contiguous() for n in ("mo", "q", "k", "v"))
+        out, attn = reference_op(impl, mo, q, k, v, c["H"], c["W"], c["h"], c["r"], c["scale"])
+        kind = "cross" if c["cross"] else "self"
+        save_case(f"stereo_tiny_{c['H']}x{c['W']}_{kind}_f16", torch.float16, c["H"], c["W"], c["h"], c["r"],
+                  c["scale"], mo, q, k, v, out, attn,
+                  f"call {last} of a MatchStereo-tiny forward at 192x192, torch seed 21, batch item 0, cast to f16")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF", "/root/reference"))
+    ap.add_argument("--skip-model", action="store_true")
+    a = ap.parse_args()
+    impl, blocks = import_reference(a.ref)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    synthetic_cases(impl, blocks)
+    if not a.skip_model:
+        model_cases(a.ref, impl)
+
+
+if __name__ == "__main__":
+    main()
