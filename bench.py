@@ -1,0 +1,331 @@
+"""Benchmark of the MatchAttention operator on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the fused operator over one batch of synthetic input.
+The default workload is the headline configuration: B=4 items of a 384x384
+token map (a 1536x1536 pair at 1/4 resolution), C=128 as 8 heads x 16, 3x3
+sub-windows (r=1), float16, flow-like offsets uniform in +-24 tokens shared by
+the heads, 10 % of the queries left unclamped next to a border.  With N GPUs
+every rank processes its own batch (independent pairs, no collective): weak
+scaling.  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU restatement of the reference's algorithm
+(oracle/) on the host cores instead, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: B, H, W, h, hd, r, dtype, kind, spread (tokens), border_frac, per_head
+    "op_384x384_b4_h8x16_r1_f16_flow": (4, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, False),
+    "op_384x384_b4_h8x16_r1_f32_flow": (4, 384, 384, 8, 16, 1, torch.float32, "flow", 24.0, 0.1, False),
+    "op_384x384_b4_h8x16_r1_f16_flow_perhead": (4, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, True),
+    "op_384x384_b4_h8x16_r1_f16_smooth": (4, 384, 384, 8, 16, 1, torch.float16, "self", 3.0, 0.0, True),
+    "op_104x208_b1_h8x16_r1_f32_cross": (1, 104, 208, 8, 16, 1, torch.float32, "cross", 16.0, 0.0, False),
+}
+DEFAULT_WORKLOAD = "op_384x384_b4_h8x16_r1_f16_flow"
+DTYPE_NAME = {torch.float16: "f16", torch.float32: "f32", torch.bfloat16: "bf16"}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes_per_query(h, hd, r, esize, with_attn=True):
+    """q + k + v + out once each, the offsets, and attn_out: s*(4C + 2h + h*M)."""
+    C, M = h * hd, (2 * r + 2) ** 2
+    return esize * (4 * C + 2 * h + (h * M if with_attn else 0))
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, MEASURED_PEAKS.json absent)"
+
+
+def ncu_traffic_per_launch(workload):
+    """dram bytes read+written per launch from the committed ncu summary, if one exists."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f).get(workload)
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons of one GPU through NVML (read-only)."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost"}
+
+    def __init__(self, index, period=0.02):
+        self.samples, self.period, self._stop = [], period, threading.Event()
+        self.max_mhz, self.ok = None, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = torch.cuda.get_device_properties(index).uuid
+            try:
+                self.dev = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nv = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                mhz = self.nv.nvmlDeviceGetClockInfo(self.dev, self.nv.NVML_CLOCK_SM)
+                try:
+                    mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.dev)
+                except Exception:
+                    mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev)
+                self.samples.append((time.perf_counter(), mhz, mask))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.ok:
+            self.thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self.ok:
+            self.thread.join(timeout=1.0)
+
+    def summary(self, t0, t1):
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        window = "timed region"
+        if len(inside) < 3:
+            inside, window = self.samples, "whole run (timed region shorter than 3 samples)"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "window": "no samples"}
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        reasons = [name for bit, name in self.REASONS.items() if mask & bit]
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(inside), "window": window}
+
+
+def make_workload(name, seed):
+    from _cases import make_inputs
+    B, H, W, h, hd, r, dtype, kind, spread, border, per_head = WORKLOADS[name]
+    mo, q, k, v = make_inputs(seed, B, H, W, h, hd, r, dtype, kind=kind, spread=spread, border_frac=border,
+                              per_head=per_head)
+    return dict(B=B, H=H, W=W, h=h, hd=hd, r=r, dtype=dtype, scale=hd ** -0.5, inputs=(mo, q, k, v))
+
+
+def time_cpu_port(wl, budget_s=12.0, nthreads=0):
+    """The oracle port on the host cores over one batch item of the workload, repeated."""
+    import oracle
+    mo, q, k, v = (t[:1].contiguous() for t in wl["inputs"])
+    H, W, r = wl["H"], wl["W"], wl["r"]
+    oracle.forward(mo, q, k, v, H, W, r, wl["scale"], nthreads=nthreads)      # warm-up (builds tables)
+    reps, t_total = 0, 0.0
+    while reps < 3 or (t_total < budget_s and reps < 50):
+        t0 = time.perf_counter()
+        oracle.forward(mo, q, k, v, H, W, r, wl["scale"], nthreads=nthreads)
+        t_total += time.perf_counter() - t0
+        reps += 1
+    cores = nthreads if nthreads > 0 else oracle.max_threads()
+    return H * W * reps / t_total, cores, reps, t_total
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    wl = make_workload(args.workload, 1234)
+    import oracle
+    H, W, r = wl["H"], wl["W"], wl["r"]
+    mo, q, k, v = (t[:1].contiguous() for t in wl["inputs"])
+    cores = oracle.max_threads()
+    for _ in range(max(1, min(args.warmup, 3))):
+        oracle.forward(mo, q, k, v, H, W, r, wl["scale"])
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.forward(mo, q, k, v, H, W, r, wl["scale"])
+    dt = time.perf_counter() - t0
+    value = H * W * steps / dt
+    sample = f"one batch item ({H * W} queries) of the workload per step, {steps} steps, {DTYPE_NAME[wl['dtype']]} " \
+             f"arithmetic emulated with the reference's rounding points"
+    line = {"impl": "reference", "metric": "matchattention_queries_per_s", "value": value, "unit": "queries/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_NAME[wl["dtype"]],
+            "data": "synthetic", "config": config_dict(args.workload, wl),
+            "cpu_baseline": {"value": value, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(name, wl):
+    return {"workload": name, "B_per_gpu": wl["B"], "token_map": [wl["H"], wl["W"]], "heads": wl["h"],
+            "head_dim": wl["hd"], "win_r": wl["r"], "window_taps": (2 * wl["r"] + 2) ** 2,
+            "l2": "inputs+outputs of one step exceed the 126 MB L2; no flush between steps"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--tile-w", type=int, default=0)
+    ap.add_argument("--chunks-per-lane", type=int, default=0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import matchattention_b200 as ma   # raises if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    wl = make_workload(args.workload, 1234 + rank)
+    B, H, W, h, hd, r, dtype = (wl[n] for n in ("B", "H", "W", "h", "hd", "r", "dtype"))
+    M = (2 * r + 2) ** 2
+    host = [t.pin_memory() for t in wl["inputs"]]
+    mo, q, k, v = (t.to(dev) for t in host)
+    out = torch.empty_like(q)
+    attn = q.new_empty(B, H * W, h, M)
+    knobs = dict(tile_w=args.tile_w, chunks_per_lane=args.chunks_per_lane)
+
+    def step():
+        ma.launch(mo, q, k, v, out, attn, H, W, (r, r), "l1_norm", wl["scale"], **knobs)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+
+    # ---- device-resident timing: exactly K steps between two events on the launching stream
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.perf_counter()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    ms_total = ev0.elapsed_time(ev1)
+    if dist is not None:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    queries_per_step = B * H * W * world
+    value = queries_per_step / (ms_per_step * 1e-3)
+
+    # ---- end to end: pinned host inputs -> device, kernel, outputs -> pinned host, every step
+    e2e = None
+    if not args.no_e2e:
+        host_out = torch.empty(out.shape, dtype=dtype).pin_memory()
+        host_attn = torch.empty(attn.shape, dtype=dtype).pin_memory()
+        d_in = [torch.empty_like(t, device=dev) for t in host]
+        h2d = sum(t.numel() * t.element_size() for t in host)
+        d2h = host_out.numel() * host_out.element_size() + host_attn.numel() * host_attn.element_size()
+
+        def e2e_step():
+            for d, s in zip(d_in, host):
+                d.copy_(s, non_blocking=True)
+            ma.launch(d_in[0], d_in[1], d_in[2], d_in[3], out, attn, H, W, (r, r), "l1_norm", wl["scale"], **knobs)
+            host_out.copy_(out, non_blocking=True)
+            host_attn.copy_(attn, non_blocking=True)
+
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        ev0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        ev1.record()
+        barrier()
+        ms_e2e = ev0.elapsed_time(ev1)
+        if dist is not None:
+            t = torch.tensor([ms_e2e], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e2e = float(t.item())
+        e2e = {"value": queries_per_step / (ms_e2e / e2e_steps * 1e-3), "unit": "queries/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "ms_per_step": ms_e2e / e2e_steps}
+    if sampler:
+        sampler.stop()
+
+    if rank == 0:
+        esize = 2 if dtype != torch.float32 else 4
+        bpq = algorithmic_bytes_per_query(h, hd, r, esize)
+        peak, peak_kind = measured_peak()
+        achieved = bpq * B * H * W / (ms_per_step * 1e-3) / 1e9     # one launch = one rank's batch
+        line = {
+            "metric": "matchattention_queries_per_s", "value": value, "unit": "queries/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_NAME[dtype], "data": "synthetic",
+            "config": config_dict(args.workload, wl),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": ncu_traffic_per_launch(args.workload), "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_query": bpq, "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "kernel": ma.describe_dispatch(h, hd, r, dtype)},
+            "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
+            "gpu_launches": args.steps,
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if not args.no_cpu_baseline:
+            cpu_qps, cores, reps, secs = time_cpu_port(wl)
+            line["cpu_baseline"] = {
+                "value": cpu_qps, "unit": "queries/s", "cores": cores, "kind": "port",
+                "sample": f"one batch item ({H * W} queries) of the workload, {reps} repetitions in {secs:.1f} s, "
+                          f"C restatement of the reference algorithm with its {DTYPE_NAME[dtype]} rounding points"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

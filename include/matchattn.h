@@ -1,0 +1,118 @@
+/*
+ * matchattn.h -- C ABI of the B200 (sm_100a) MatchAttention operator.
+ *
+ * The library replaces the native side of the reference's 'cuda' path:
+ *   - pybind entry  match_attention.fused_forward      models/src/match_former_cuda.cpp:24-44
+ *   - host driver   match_former_fused_forward          models/src/match_former_fused_forward.cu:461-628
+ * and computes what the reference's 'pytorch' path computes
+ * (models/mat_pytorch_impl.py:3-178 as driven by models/attention_blocks.py:82-91).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every buffer is owned by the caller;
+ *   - all pointers are DEVICE pointers on the current CUDA device;
+ *   - nothing is allocated, nothing is synchronised: each call enqueues its
+ *     kernels on `cuda_stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) and returns;
+ *   - outputs are fully overwritten, they need not be zeroed beforehand;
+ *   - the return value is 0 on success, otherwise a status that
+ *     matchattn_strerror() turns into text.  A bad argument never reaches the
+ *     device.
+ */
+#ifndef MATCHATTN_H_
+#define MATCHATTN_H_
+
+#if defined(__GNUC__)
+#define MATCHATTN_API __attribute__((visibility("default")))
+#else
+#define MATCHATTN_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types (argument `dtype`) */
+#define MATCHATTN_F32  0
+#define MATCHATTN_F16  1
+#define MATCHATTN_BF16 2
+
+/* scoring functions (argument `attn_type`).  Only the negative L1 distance is
+ * implemented; it is the only one the reference models select
+ * (models/attention_blocks.py:93). */
+#define MATCHATTN_L1_NORM 0
+
+/* status codes */
+#define MATCHATTN_OK                 0
+#define MATCHATTN_ERR_NULL           1  /* a required pointer is NULL                         */
+#define MATCHATTN_ERR_SHAPE          2  /* a size is <= 0, or the row band is empty / outside */
+#define MATCHATTN_ERR_WINDOW_FIT     3  /* 2r+2 exceeds H or W (models/attention_blocks.py:64) */
+#define MATCHATTN_ERR_DTYPE          4  /* unknown element type                               */
+#define MATCHATTN_ERR_ATTN_TYPE      5  /* scoring function not implemented                   */
+#define MATCHATTN_ERR_WINDOW         6  /* rx != ry, r < 0 or r above the supported maximum    */
+#define MATCHATTN_ERR_ALIGN          7  /* a pointer is not aligned to its element size       */
+#define MATCHATTN_ERR_TOO_LARGE      8  /* sizes overflow the 32-bit index ranges in use      */
+#define MATCHATTN_ERR_CUDA         100  /* 100 + cudaError_t of a failed launch               */
+
+/* largest window radius accepted */
+#define MATCHATTN_MAX_R 4
+
+/*
+ * The fused MatchAttention forward.
+ * Replaces mf_fused_forward (models/src/match_former_cuda.cpp:24-39) and the
+ * seven-launch driver behind it (models/src/match_former_fused_forward.cu:461-628).
+ *
+ *   max_offset [B, Nq, h, 2]  absolute sampling centre (x, y) of every (query, head), token units
+ *   q          [B, Nq, h*hd]
+ *   k, v       [B, H*W, h*hd]
+ *   out        [B, Nq, h*hd]                      written
+ *   attn_out   [B, Nq, h, (2r+2)^2]               written; may be NULL to skip it
+ *
+ * Nq = (q_row_end - q_row_begin) * W.  With q_row_begin = 0 and q_row_end = H
+ * this is the whole op.  Otherwise the query-side arrays (max_offset, q, out,
+ * attn_out) hold only the rows [q_row_begin, q_row_end) of the token map while
+ * k and v still hold all of it: the row-band form used to split one large
+ * pair across GPUs.
+ *
+ * Window taps outside the map are clamped to the nearest border token
+ * (models/mat_pytorch_impl.py:58-59); max_offset itself may lie anywhere.
+ * rx must equal ry.  `scale` multiplies the negative L1 score
+ * (models/attention_blocks.py:86).
+ */
+MATCHATTN_API int matchattn_fused_forward(const void *max_offset, const void *q, const void *k, const void *v,
+                            void *out, void *attn_out,
+                            int B, int H, int W, int h, int hd, int rx, int ry,
+                            int dtype, int attn_type, float scale,
+                            int q_row_begin, int q_row_end, void *cuda_stream);
+
+/*
+ * Tuning knobs for the call above; same contract and results.
+ *   tile_w        width in queries of the 2-D query tile that one thread block covers
+ *                 (0 = choose automatically);
+ *   force_generic non-zero selects the slow any-shape kernel even where a
+ *                 specialised one exists (used by the tests to cover it);
+ *   chunks_per_lane  how many 8-channel chunks of a head one lane owns (0 =
+ *                 choose automatically; a value that does not divide hd/8 into a
+ *                 power-of-two number of lanes falls back to the any-shape kernel).
+ * No counterpart in the reference.
+ */
+MATCHATTN_API int matchattn_fused_forward_ex(const void *max_offset, const void *q, const void *k, const void *v,
+                               void *out, void *attn_out,
+                               int B, int H, int W, int h, int hd, int rx, int ry,
+                               int dtype, int attn_type, float scale,
+                               int q_row_begin, int q_row_end, void *cuda_stream,
+                               int tile_w, int force_generic, int chunks_per_lane);
+
+/* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
+ * "generic", ...) or NULL if they are rejected.  Launches nothing. */
+MATCHATTN_API const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned);
+
+/* version of this ABI: major * 100 + minor */
+MATCHATTN_API int matchattn_version(void);
+
+/* text for a status code; never NULL */
+MATCHATTN_API const char *matchattn_strerror(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MATCHATTN_H_ */

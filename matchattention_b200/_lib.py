@@ -1,0 +1,53 @@
+"""ctypes binding of libmatchattn_b200.so (the C ABI in include/matchattn.h).
+
+The library is loaded from matchattention_b200/lib/.  There is no fallback: if
+it is missing, importing this module raises, and so does every op.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libmatchattn_b200.so")
+
+# every symbol include/matchattn.h declares
+EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_describe_dispatch",
+           "matchattn_version", "matchattn_strerror")
+
+F32, F16, BF16 = 0, 1, 2
+L1_NORM = 0
+
+_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build the CUDA library first with "
+            "`python -m matchattention_b200.build` (needs nvcc); there is no CPU or PyTorch fallback")
+    lib = ctypes.CDLL(LIB_PATH)
+    base = [_vp] * 6 + [_i] * 9 + [_f, _i, _i, _vp]
+    lib.matchattn_fused_forward.restype = _i
+    lib.matchattn_fused_forward.argtypes = base
+    lib.matchattn_fused_forward_ex.restype = _i
+    lib.matchattn_fused_forward_ex.argtypes = base + [_i, _i, _i]
+    lib.matchattn_describe_dispatch.restype = ctypes.c_char_p
+    lib.matchattn_describe_dispatch.argtypes = [_i] * 5
+    lib.matchattn_version.restype = _i
+    lib.matchattn_version.argtypes = []
+    lib.matchattn_strerror.restype = ctypes.c_char_p
+    lib.matchattn_strerror.argtypes = [_i]
+    return lib
+
+
+lib = _load()
+
+
+def strerror(status: int) -> str:
+    return lib.matchattn_strerror(int(status)).decode()
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise RuntimeError(f"matchattn_b200: {strerror(status)} (status {status})")

@@ -1,0 +1,527 @@
+// MatchAttention forward kernels for sm_100a.
+//
+// One launch does the whole operator: window origin and bilinear weights from
+// the sampling centre, replicate-clamped gather of the (2r+2)^2 key taps,
+// negative L1 scores, BilinearSoftmax (four shifted (2r+1)^2 softmaxes blended
+// by the bilinear weights) and the weighted sum of the value taps.  Nothing is
+// written to global memory except the two outputs.
+//
+// Work split.  A head's hd channels are cut into "chunks" of 8 channels.  One
+// lane owns CPL consecutive chunks of one head of one query; LPH lanes (a power
+// of two, inside one warp) together own a head and add their partial L1 sums
+// with xor shuffles.  The h*LPH lanes of a query sit next to each other, so a
+// warp reads and writes q / out / attn_out / max_offset as contiguous runs, and
+// a block covers a 2-D tile of queries so that neighbouring windows overlap in
+// L1.  Key/value taps are fetched straight from global memory with 128- or
+// 256-bit loads through L1/L2 (each tap of a lane is a whole number of 32-byte
+// sectors or a 16-byte half sector).
+//
+// Arithmetic.  For float16 / bfloat16 every rounding the eager PyTorch
+// evaluation of the algorithm performs is reproduced (q-k, the L1 sum, the
+// scale, the softmax result, weight*p, the four accumulating adds, a*v, the
+// final sum); all reductions accumulate in float32.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace matchattn {
+
+constexpr int kThreads = 256;
+
+struct Params {
+    const void *mo, *q, *k, *v;
+    void *out, *attn;
+    int B, H, W, h, hd, C;
+    int rows;       // query rows of the band
+    int Nq;         // rows * W
+    int N;          // H * W
+    int r;          // window radius (generic kernel only)
+    int lph;        // lanes per head
+    int lph_shift;  // log2(lph)
+    int G;          // lanes per query = h * lph
+    int tile_w;     // query tile of a block: tile_w (power of two) x tile_h
+    int tile_w_shift;
+    int tile_h;
+    int tiles_x;
+    float scale;
+};
+
+// ------------------------------------------------------------------ loads / stores
+
+__device__ __forceinline__ void ld_nc_256(uint32_t *w, const void *p)
+{
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void ld_nc_128(uint32_t *w, const void *p)
+{
+    asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_256(void *p, const uint32_t *w)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+__device__ __forceinline__ void st_128(void *p, const uint32_t *w)
+{
+    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                 : "memory");
+}
+__device__ __forceinline__ void st_64(void *p, const uint32_t *w)
+{
+    asm volatile("st.global.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(w[0]), "r"(w[1]) : "memory");
+}
+
+// NW 32-bit words from an address aligned to 32 bytes when NW % 8 == 0, else to 16 bytes.
+template <int NW>
+__device__ __forceinline__ void load_words(uint32_t (&w)[NW], const void *p)
+{
+    static_assert(NW % 4 == 0, "a lane's slice is a multiple of 16 bytes");
+    if constexpr (NW % 8 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 8; ++i) ld_nc_256(&w[8 * i], static_cast<const char *>(p) + 32 * i);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NW / 4; ++i) ld_nc_128(&w[4 * i], static_cast<const char *>(p) + 16 * i);
+    }
+}
+
+// NW words to an address whose alignment is the largest of 32/16/8 bytes dividing 4*NW.
+template <int NW>
+__device__ __forceinline__ void store_words(void *p, const uint32_t (&w)[NW])
+{
+    static_assert(NW % 2 == 0, "stores are at least 8 bytes wide");
+    if constexpr (NW % 8 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 8; ++i) st_256(static_cast<char *>(p) + 32 * i, &w[8 * i]);
+    } else if constexpr (NW % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 4; ++i) st_128(static_cast<char *>(p) + 16 * i, &w[4 * i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NW / 2; ++i) st_64(static_cast<char *>(p) + 8 * i, &w[2 * i]);
+    }
+}
+
+// ------------------------------------------------------------------ per-dtype arithmetic
+
+template <typename T>
+struct DT;
+
+template <>
+struct DT<float> {
+    static constexpr int kWordsPerChunk = 8;   // 8 channels * 4 bytes
+    static constexpr int kElemsPerWord = 1;
+    static __device__ __forceinline__ float rnd(float x) { return x; }
+    static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
+    {
+        const float2 t = __ldg(static_cast<const float2 *>(p));
+        x = t.x;
+        y = t.y;
+    }
+    // acc += |q - k| over the elements of one word
+    static __device__ __forceinline__ void absdiff(float &a0, float &, uint32_t qw, uint32_t kw)
+    {
+        a0 += fabsf(__uint_as_float(qw) - __uint_as_float(kw));
+    }
+    using Bcast = float;
+    static __device__ __forceinline__ Bcast bcast(float a) { return a; }
+    // o += a * v over the elements of one word (o points at this word's accumulators)
+    static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o) { o[0] = fmaf(a, __uint_as_float(vw), o[0]); }
+    static __device__ __forceinline__ uint32_t pack(const float *o) { return __float_as_uint(o[0]); }
+    using A = float;  // storage type of the attention weights
+    static __device__ __forceinline__ A a_zero() { return 0.f; }
+    static __device__ __forceinline__ A a_from(float x) { return x; }
+    static __device__ __forceinline__ float a_to(A a) { return a; }
+    static __device__ __forceinline__ A a_mul(A x, A y) { return x * y; }
+    static __device__ __forceinline__ A a_add(A x, A y) { return x + y; }
+    static __device__ __forceinline__ uint32_t a_pack(const A *a) { return __float_as_uint(a[0]); }
+};
+
+template <>
+struct DT<__half> {
+    static constexpr int kWordsPerChunk = 4;   // 8 channels * 2 bytes
+    static constexpr int kElemsPerWord = 2;
+    static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); }
+    static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
+    {
+        const uint32_t u = __ldg(static_cast<const uint32_t *>(p));
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u));
+        x = f.x;
+        y = f.y;
+    }
+    static __device__ __forceinline__ void absdiff(float &a0, float &a1, uint32_t qw, uint32_t kw)
+    {
+        const __half2 d = __habs2(__hsub2(*reinterpret_cast<const __half2 *>(&qw), *reinterpret_cast<const __half2 *>(&kw)));
+        const float2 f = __half22float2(d);
+        a0 += f.x;
+        a1 += f.y;
+    }
+    using Bcast = __half2;
+    static __device__ __forceinline__ Bcast bcast(__half a) { return __half2half2(a); }
+    static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o)
+    {
+        const float2 f = __half22float2(__hmul2(a, *reinterpret_cast<const __half2 *>(&vw)));
+        o[0] += f.x;
+        o[1] += f.y;
+    }
+    static __device__ __forceinline__ uint32_t pack(const float *o)
+    {
+        const __half2 t = __floats2half2_rn(o[0], o[1]);
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    using A = __half;
+    static __device__ __forceinline__ A a_zero() { return __ushort_as_half(0); }
+    static __device__ __forceinline__ A a_from(float x) { return __float2half_rn(x); }
+    static __device__ __forceinline__ float a_to(A a) { return __half2float(a); }
+    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul(x, y); }
+    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd(x, y); }
+    static __device__ __forceinline__ uint32_t a_pack(const A *a)
+    {
+        const __half2 t = __halves2half2(a[0], a[1]);
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+};
+
+template <>
+struct DT<__nv_bfloat16> {
+    static constexpr int kWordsPerChunk = 4;
+    static constexpr int kElemsPerWord = 2;
+    static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
+    {
+        const uint32_t u = __ldg(static_cast<const uint32_t *>(p));
+        x = __uint_as_float(u << 16);
+        y = __uint_as_float(u & 0xffff0000u);
+    }
+    static __device__ __forceinline__ void absdiff(float &a0, float &a1, uint32_t qw, uint32_t kw)
+    {
+        const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&qw),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&kw));
+        const uint32_t u = *reinterpret_cast<const uint32_t *>(&d);
+        a0 += fabsf(__uint_as_float(u << 16));
+        a1 += fabsf(__uint_as_float(u & 0xffff0000u));
+    }
+    using Bcast = __nv_bfloat162;
+    static __device__ __forceinline__ Bcast bcast(__nv_bfloat16 a) { return __bfloat162bfloat162(a); }
+    static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o)
+    {
+        const __nv_bfloat162 t = __hmul2(a, *reinterpret_cast<const __nv_bfloat162 *>(&vw));
+        const uint32_t u = *reinterpret_cast<const uint32_t *>(&t);
+        o[0] += __uint_as_float(u << 16);
+        o[1] += __uint_as_float(u & 0xffff0000u);
+    }
+    static __device__ __forceinline__ uint32_t pack(const float *o)
+    {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(o[0], o[1]);
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    using A = __nv_bfloat16;
+    static __device__ __forceinline__ A a_zero() { return __ushort_as_bfloat16(0); }
+    static __device__ __forceinline__ A a_from(float x) { return __float2bfloat16_rn(x); }
+    static __device__ __forceinline__ float a_to(A a) { return __bfloat162float(a); }
+    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul(x, y); }
+    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd(x, y); }
+    static __device__ __forceinline__ uint32_t a_pack(const A *a)
+    {
+        const __nv_bfloat162 t = __halves2bfloat162(a[0], a[1]);
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+};
+
+// ------------------------------------------------------------------ shared pieces
+
+// Window origin: floor of the centre, limited to the range in which the
+// replicate clamp of the taps cannot tell the difference (keeps the int
+// conversion defined for huge or NaN centres; NaN still poisons the weights).
+__device__ __forceinline__ int window_origin(float fl, int r, int extent)
+{
+    return static_cast<int>(fminf(fmaxf(fl, static_cast<float>(-(r + 2))), static_cast<float>(extent + r + 1)));
+}
+
+// Bilinear weights nw, ne, sw, se, each rounded to T where the reference rounds.
+template <typename T>
+__device__ __forceinline__ void bilinear_weights(float x, float xf, float y, float yf, float (&w)[4])
+{
+    const float dx = DT<T>::rnd(x - xf), dy = DT<T>::rnd(y - yf);
+    const float ex = DT<T>::rnd(1.f - dx), ey = DT<T>::rnd(1.f - dy);
+    w[0] = DT<T>::rnd(ex * ey);
+    w[1] = DT<T>::rnd(dx * ey);
+    w[2] = DT<T>::rnd(ex * dy);
+    w[3] = DT<T>::rnd(dx * dy);
+}
+
+// Raw L1 sums -> scaled scores, with the reference's roundings.
+template <typename T>
+__device__ __forceinline__ float finish_score(float l1, float scale)
+{
+    return DT<T>::rnd(DT<T>::rnd(-l1) * scale);
+}
+
+// BilinearSoftmax over a (2R+2)^2 score window held in registers.
+template <typename T, int R>
+__device__ __forceinline__ void bilinear_softmax(const float (&s)[(2 * R + 2) * (2 * R + 2)], const float (&w)[4],
+                                                 typename DT<T>::A (&a)[(2 * R + 2) * (2 * R + 2)])
+{
+    constexpr int SIDE = 2 * R + 2, SUB = 2 * R + 1, M = SIDE * SIDE;
+    using A = typename DT<T>::A;
+#pragma unroll
+    for (int m = 0; m < M; ++m) a[m] = DT<T>::a_zero();
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int oy = t >> 1, ox = t & 1;
+        float mx = s[oy * SIDE + ox];
+#pragma unroll
+        for (int j = 0; j < SUB; ++j)
+#pragma unroll
+            for (int i = 0; i < SUB; ++i) mx = fmaxf(mx, s[(j + oy) * SIDE + i + ox]);
+        float e[SUB * SUB];
+        float den = 0.f;
+#pragma unroll
+        for (int j = 0; j < SUB; ++j)
+#pragma unroll
+            for (int i = 0; i < SUB; ++i) {
+                const float ev = __expf(s[(j + oy) * SIDE + i + ox] - mx);
+                e[j * SUB + i] = ev;
+                den += ev;
+            }
+        const float inv = __frcp_rn(den);
+        const A wt = DT<T>::a_from(w[t]);
+#pragma unroll
+        for (int j = 0; j < SUB; ++j)
+#pragma unroll
+            for (int i = 0; i < SUB; ++i) {
+                const int m = (j + oy) * SIDE + i + ox;
+                const A p = DT<T>::a_from(e[j * SUB + i] * inv);
+                a[m] = DT<T>::a_add(a[m], DT<T>::a_mul(wt, p));
+            }
+    }
+}
+
+// ------------------------------------------------------------------ the specialised kernel
+
+template <typename T, int R, int CPL, bool MULTI>
+__global__ void __launch_bounds__(kThreads) fused_forward_kernel(const Params p)
+{
+    constexpr int SIDE = 2 * R + 2, M = SIDE * SIDE;
+    constexpr int NW = CPL * DT<T>::kWordsPerChunk;        // 32-bit words of K (or V, q, out) per lane and tap
+    constexpr int EPW = DT<T>::kElemsPerWord;
+    constexpr int SLICE = CPL * 8;                          // channels per lane
+    using A = typename DT<T>::A;
+
+    // lane -> (query of the tile, head, slice of the head)
+    const int tid = threadIdx.x;
+    const int lq = tid / p.G;
+    const int g = tid - lq * p.G;
+    int head, sl;
+    if constexpr (MULTI) {
+        head = g >> p.lph_shift;
+        sl = g & (p.lph - 1);
+    } else {
+        head = g;
+        sl = 0;
+    }
+    const int tile_y = blockIdx.x / p.tiles_x;
+    const int tile_x = blockIdx.x - tile_y * p.tiles_x;
+    int qx = tile_x * p.tile_w + (lq & (p.tile_w - 1));
+    int qy = tile_y * p.tile_h + (lq >> p.tile_w_shift);
+    const bool valid = (lq >> p.tile_w_shift) < p.tile_h && qx < p.W && qy < p.rows;
+    if constexpr (!MULTI) {
+        if (!valid) return;
+    } else {
+        // lanes without a query stay for the shuffles and redo a neighbour's work
+        qx = min(qx, p.W - 1);
+        qy = min(qy, p.rows - 1);
+    }
+    const int b = blockIdx.y;
+    const int64_t bq = static_cast<int64_t>(b) * p.Nq + qy * p.W + qx;
+
+    // sampling centre -> origin, weights, clamped tap rows / columns (in elements)
+    float x, y;
+    DT<T>::load_xy(static_cast<const T *>(p.mo) + (bq * p.h + head) * 2, x, y);
+    const float xf = floorf(x), yf = floorf(y);
+    float wgt[4];
+    bilinear_weights<T>(x, xf, y, yf, wgt);
+    const int x0 = window_origin(xf, R, p.W) - R, y0 = window_origin(yf, R, p.H) - R;
+    int col[SIDE], row[SIDE];
+#pragma unroll
+    for (int i = 0; i < SIDE; ++i) {
+        col[i] = min(max(x0 + i, 0), p.W - 1) * p.C;
+        row[i] = min(max(y0 + i, 0), p.H - 1) * p.W * p.C;
+    }
+
+    const int lane_off = head * p.hd + sl * SLICE;
+    const int64_t kv_base = static_cast<int64_t>(b) * p.N * p.C + lane_off;
+    const T *kb = static_cast<const T *>(p.k) + kv_base;
+    const T *vb = static_cast<const T *>(p.v) + kv_base;
+
+    uint32_t qw[NW];
+    load_words<NW>(qw, static_cast<const T *>(p.q) + bq * p.C + lane_off);
+
+    // scores
+    float s[M];
+#pragma unroll
+    for (int j = 0; j < SIDE; ++j)
+#pragma unroll
+        for (int i = 0; i < SIDE; ++i) {
+            uint32_t kw[NW];
+            load_words<NW>(kw, kb + (row[j] + col[i]));
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                if (EPW == 1 && (w & 1)) DT<T>::absdiff(a1, a0, qw[w], kw[w]);
+                else DT<T>::absdiff(a0, a1, qw[w], kw[w]);
+            }
+            float part = a0 + a1;
+            if constexpr (MULTI) {
+                for (int o = p.lph >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            }
+            s[j * SIDE + i] = finish_score<T>(part, p.scale);
+        }
+
+    A a[M];
+    bilinear_softmax<T, R>(s, wgt, a);
+
+    if (p.attn != nullptr && sl == 0 && valid) {
+        constexpr int NWA = M / EPW;
+        uint32_t aw[NWA];
+#pragma unroll
+        for (int w = 0; w < NWA; ++w) aw[w] = DT<T>::a_pack(&a[w * EPW]);
+        store_words<NWA>(static_cast<T *>(p.attn) + (bq * p.h + head) * M, aw);
+    }
+
+    // weighted sum of the value taps
+    float o[NW * EPW];
+#pragma unroll
+    for (int c = 0; c < NW * EPW; ++c) o[c] = 0.f;
+#pragma unroll
+    for (int j = 0; j < SIDE; ++j)
+#pragma unroll
+        for (int i = 0; i < SIDE; ++i) {
+            uint32_t vw[NW];
+            load_words<NW>(vw, vb + (row[j] + col[i]));
+            const typename DT<T>::Bcast am = DT<T>::bcast(a[j * SIDE + i]);
+#pragma unroll
+            for (int w = 0; w < NW; ++w) DT<T>::wmul(am, vw[w], &o[w * EPW]);
+        }
+
+    if (valid) {
+        uint32_t ow[NW];
+#pragma unroll
+        for (int w = 0; w < NW; ++w) ow[w] = DT<T>::pack(&o[w * EPW]);
+        store_words<NW>(static_cast<T *>(p.out) + bq * p.C + lane_off, ow);
+    }
+}
+
+// ------------------------------------------------------------------ the any-shape kernel
+//
+// One thread per (query, head); scalar loads; any head width, any radius up to
+// kMaxR, pointers aligned to the element size only.  Slow: the fallback for
+// shapes the specialised kernel does not cover.
+
+constexpr int kMaxR = 4;
+constexpr int kMaxTaps = (2 * kMaxR + 2) * (2 * kMaxR + 2);
+
+template <typename T>
+__device__ __forceinline__ float load_one(const T *p);
+template <>
+__device__ __forceinline__ float load_one<float>(const float *p) { return __ldg(p); }
+template <>
+__device__ __forceinline__ float load_one<__half>(const __half *p) { return __half2float(__ldg(p)); }
+template <>
+__device__ __forceinline__ float load_one<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat162float(__ldg(p)); }
+
+template <typename T>
+__device__ __forceinline__ void store_one(T *p, float x);
+template <>
+__device__ __forceinline__ void store_one<float>(float *p, float x) { *p = x; }
+template <>
+__device__ __forceinline__ void store_one<__half>(__half *p, float x) { *p = __float2half_rn(x); }
+template <>
+__device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16 *p, float x) { *p = __float2bfloat16_rn(x); }
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params p)
+{
+    const int64_t per_item = static_cast<int64_t>(p.Nq) * p.h;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    if (t >= per_item) return;
+    const int b = blockIdx.y;
+    const int head = static_cast<int>(t % p.h);
+    const int64_t bq = static_cast<int64_t>(b) * p.Nq + t / p.h;
+    const int r = p.r, side = 2 * r + 2, sub = 2 * r + 1, M = side * side;
+
+    const T *mo = static_cast<const T *>(p.mo) + (bq * p.h + head) * 2;
+    const float x = load_one<T>(mo), y = load_one<T>(mo + 1);
+    const float xf = floorf(x), yf = floorf(y);
+    float wgt[4];
+    bilinear_weights<T>(x, xf, y, yf, wgt);
+    const int x0 = window_origin(xf, r, p.W) - r, y0 = window_origin(yf, r, p.H) - r;
+
+    const T *qp = static_cast<const T *>(p.q) + bq * p.C + head * p.hd;
+    const int64_t kv_base = static_cast<int64_t>(b) * p.N * p.C + head * p.hd;
+    const T *kb = static_cast<const T *>(p.k) + kv_base;
+    const T *vb = static_cast<const T *>(p.v) + kv_base;
+
+    float s[kMaxTaps], a[kMaxTaps];
+    for (int j = 0; j < side; ++j) {
+        const int ty = min(max(y0 + j, 0), p.H - 1);
+        for (int i = 0; i < side; ++i) {
+            const int tx = min(max(x0 + i, 0), p.W - 1);
+            const T *kp = kb + static_cast<int64_t>(ty * p.W + tx) * p.C;
+            float acc = 0.f;
+            for (int c = 0; c < p.hd; ++c) acc += fabsf(DT<T>::rnd(load_one<T>(qp + c) - load_one<T>(kp + c)));
+            s[j * side + i] = finish_score<T>(acc, p.scale);
+            a[j * side + i] = 0.f;
+        }
+    }
+    for (int tq = 0; tq < 4; ++tq) {
+        const int oy = tq >> 1, ox = tq & 1;
+        float mx = s[oy * side + ox];
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) mx = fmaxf(mx, s[(j + oy) * side + i + ox]);
+        float den = 0.f;
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) den += __expf(s[(j + oy) * side + i + ox] - mx);
+        const float inv = __frcp_rn(den);
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) {
+                const int m = (j + oy) * side + i + ox;
+                const float pr = DT<T>::rnd(__expf(s[m] - mx) * inv);
+                a[m] = DT<T>::rnd(a[m] + DT<T>::rnd(wgt[tq] * pr));
+            }
+    }
+    if (p.attn != nullptr) {
+        T *ap = static_cast<T *>(p.attn) + (bq * p.h + head) * M;
+        for (int m = 0; m < M; ++m) store_one<T>(ap + m, a[m]);
+    }
+    T *op = static_cast<T *>(p.out) + bq * p.C + head * p.hd;
+    for (int c = 0; c < p.hd; ++c) {
+        float acc = 0.f;
+        for (int j = 0; j < side; ++j) {
+            const int ty = min(max(y0 + j, 0), p.H - 1);
+            for (int i = 0; i < side; ++i) {
+                const int tx = min(max(x0 + i, 0), p.W - 1);
+                const float vv = load_one<T>(vb + static_cast<int64_t>(ty * p.W + tx) * p.C + c);
+                if (sizeof(T) == 4) acc = fmaf(a[j * side + i], vv, acc);
+                else acc += DT<T>::rnd(a[j * side + i] * vv);
+            }
+        }
+        store_one<T>(op + c, acc);
+    }
+}
+
+// Launchers, one translation unit per element type.
+template <typename T>
+cudaError_t launch_fast(const Params &p, int r, int cpl, bool multi, dim3 grid, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_generic(const Params &p, dim3 grid, cudaStream_t stream);
+
+}  // namespace matchattn

@@ -1,0 +1,154 @@
+"""Host side of the B200 MatchAttention operator.
+
+Mirrors the reference's operator interface for this path
+(models/match_former_ops.py and the native module it imports):
+
+* :func:`fused_forward` -- same 12 positional arguments and in-place contract
+  as ``match_attention.fused_forward`` (models/src/match_former_cuda.cpp:24-44);
+* ``torch.ops.matchattn_b200.fused_forward_ops`` -- opaque custom op with a fake
+  kernel, the counterpart of ``match_attention::fused_forward_ops``
+  (models/match_former_ops.py:6-62);
+* :class:`MF_FusedForwardOps` -- module with the reference's ``forward``
+  signature and return values (models/match_former_ops.py:65-121).
+
+Differences, all on the safe side: arguments are validated (shape, dtype,
+device, contiguity) and violations raise; the launch goes to PyTorch's current
+stream; nothing is allocated or synchronised inside the call; outputs need not
+be zero-filled.  Inputs must be CUDA tensors: there is no CPU path.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+_DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _window_radius(win_r) -> Tuple[int, int]:
+    if isinstance(win_r, int):
+        return win_r, win_r
+    if len(win_r) != 2:
+        raise ValueError(f"win_r must have two entries, got {win_r!r}")
+    return int(win_r[0]), int(win_r[1])
+
+
+def _check_tensors(max_offset, q, k, v, output, attn_out, H, W, rows, attn_num):
+    if not q.is_cuda:
+        raise RuntimeError("matchattn_b200 runs on CUDA tensors only (no CPU fallback); got device " + str(q.device))
+    if q.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {q.dtype}: float32, float16 or bfloat16")
+    if q.dim() != 3 or max_offset.dim() != 4 or max_offset.size(-1) != 2:
+        raise ValueError("expected q [B,N,C] and max_offset [B,N,h,2]")
+    B, Nq, C = q.shape
+    h = max_offset.size(2)
+    if C % h != 0:
+        raise ValueError(f"C={C} is not a multiple of the head count h={h}")
+    if Nq != rows * W:
+        raise ValueError(f"q has {Nq} queries per item, expected rows*W = {rows}*{W}")
+    expect = {"max_offset": (max_offset, (B, Nq, h, 2)), "k": (k, (B, H * W, C)), "v": (v, (B, H * W, C)),
+              "output": (output, (B, Nq, C))}
+    if attn_out is not None:
+        expect["attn_out"] = (attn_out, (B, Nq, h, attn_num))
+    expect["q"] = (q, (B, Nq, C))
+    for name, (t, shape) in expect.items():
+        if tuple(t.shape) != shape:
+            raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {shape}")
+        if t.dtype != q.dtype:
+            raise TypeError(f"{name} has dtype {t.dtype}, expected {q.dtype}")
+        if t.device != q.device:
+            raise RuntimeError(f"{name} is on {t.device}, expected {q.device}")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    return B, h, C // h
+
+
+def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_type: str = "l1_norm",
+           scale: float = 1.0, q_row_begin: int = 0, q_row_end: Optional[int] = None, *,
+           tile_w: int = 0, force_generic: bool = False, chunks_per_lane: int = 0) -> None:
+    """Validate, then enqueue the fused kernel on the current stream of q's device.
+
+    ``attn_out`` may be None (the attention weights are then not written).  With
+    a row band, the query-side tensors hold rows [q_row_begin, q_row_end) only.
+    """
+    rx, ry = _window_radius(win_r)
+    if q_row_end is None:
+        q_row_end = H
+    if attn_type != "l1_norm":
+        raise NotImplementedError(f"attn_type {attn_type!r}: only 'l1_norm' is implemented")
+    attn_num = (2 * rx + 2) * (2 * ry + 2)
+    B, h, hd = _check_tensors(max_offset, q, k, v, output, attn_out, H, W, q_row_end - q_row_begin, attn_num)
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        status = _lib.lib.matchattn_fused_forward_ex(
+            max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
+            attn_out.data_ptr() if attn_out is not None else None,
+            B, H, W, h, hd, rx, ry, _DTYPE_CODE[q.dtype], _lib.L1_NORM, float(scale),
+            q_row_begin, q_row_end, stream, int(tile_w), int(bool(force_generic)), int(chunks_per_lane))
+    _lib.check(status)
+
+
+def fused_forward(max_offset, q, k, v, output, attn_out, H, W, win_r, attn_num, attn_type, scale) -> None:
+    """Drop-in for ``match_attention.fused_forward`` (same 12 positional arguments,
+    writes ``output`` and ``attn_out`` in place, returns None)."""
+    rx, ry = _window_radius(win_r)
+    if attn_num != (2 * rx + 2) * (2 * ry + 2):
+        raise ValueError(f"attn_num={attn_num} does not match win_r={list(win_r)}")
+    launch(max_offset, q, k, v, output, attn_out, int(H), int(W), (rx, ry), attn_type, float(scale))
+
+
+@torch.library.custom_op("matchattn_b200::fused_forward_ops", mutates_args={"output", "attn_out"})
+def fused_forward_ops(max_offset: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                      output: torch.Tensor, attn_out: torch.Tensor, H: int, W: int, win_r: List[int],
+                      attn_num: int, attn_type: str, scale: float) -> None:
+    fused_forward(max_offset, q, k, v, output, attn_out, H, W, win_r, attn_num, attn_type, scale)
+
+
+@fused_forward_ops.register_fake
+def _(max_offset, q, k, v, output, attn_out, H, W, win_r, attn_num, attn_type, scale):
+    B, N, C = q.shape
+    h = max_offset.size(2)
+    torch._check(output.shape == (B, N, C), lambda: f"output shape {output.shape}, expected {(B, N, C)}")
+    torch._check(attn_out.shape == (B, N, h, attn_num),
+                 lambda: f"attn_out shape {attn_out.shape}, expected {(B, N, h, attn_num)}")
+    torch._check(output.dtype == q.dtype and attn_out.dtype == q.dtype, lambda: "output dtypes must equal q's")
+    torch._check(output.device == q.device and attn_out.device == q.device, lambda: "outputs must be on q's device")
+    return None
+
+
+class MF_FusedForwardOps(nn.Module):
+    """Same call and return values as the reference module of this name
+    (models/match_former_ops.py:65-121); outputs are allocated uninitialised
+    because the kernel overwrites every element."""
+
+    def forward(self, max_offset: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, H: int, W: int,
+                win_r: List[int], attn_num: int, attn_type: str = "l1_norm",
+                scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+        B, N, _ = q.shape
+        h = max_offset.size(2)
+        output = torch.empty_like(v)
+        attn_out = q.new_empty([B, N, h, attn_num])
+        fused_forward_ops(max_offset, q, k, v, output, attn_out, H, W, list(win_r), attn_num, attn_type, scale)
+        return output, attn_out
+
+
+def match_attention(max_offset, q, k, v, H: int, W: int, r: int, scale: float, *, need_attn: bool = True,
+                    q_row_begin: int = 0, q_row_end: Optional[int] = None, out=None, attn_out=None, **knobs):
+    """Functional form: allocates (or reuses) the outputs and returns (out, attn or None)."""
+    B, Nq, _ = q.shape
+    h = max_offset.size(2)
+    if out is None:
+        out = torch.empty_like(q)
+    if need_attn and attn_out is None:
+        attn_out = q.new_empty([B, Nq, h, (2 * r + 2) ** 2])
+    launch(max_offset, q, k, v, out, attn_out if need_attn else None, H, W, (r, r), "l1_norm", scale,
+           q_row_begin, q_row_end, **knobs)
+    return out, (attn_out if need_attn else None)
+
+
+def describe_dispatch(h: int, hd: int, r: int, dtype: torch.dtype, aligned32: bool = True) -> Optional[str]:
+    res = _lib.lib.matchattn_describe_dispatch(h, hd, r, _DTYPE_CODE[dtype], int(aligned32))
+    return res.decode() if res is not None else None
