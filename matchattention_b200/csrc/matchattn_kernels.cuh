@@ -110,6 +110,13 @@ __device__ __forceinline__ void store_words(void *p, const uint32_t (&w)[NW])
     }
 }
 
+// float32 accumulator += float16 addend in one instruction (PTX ISA 8.6, sm_100+)
+__device__ __forceinline__ float add_f32_f16(float acc, unsigned short h)
+{
+    asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc) : "h"(h));
+    return acc;
+}
+
 // ------------------------------------------------------------------ per-dtype arithmetic
 
 template <typename T>
@@ -119,6 +126,7 @@ template <>
 struct DT<float> {
     static constexpr int kWordsPerChunk = 8;   // 8 channels * 4 bytes
     static constexpr int kElemsPerWord = 1;
+    static constexpr bool kHalfPipe = false;
     static __device__ __forceinline__ float rnd(float x) { return x; }
     static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
     {
@@ -149,6 +157,7 @@ template <>
 struct DT<__half> {
     static constexpr int kWordsPerChunk = 4;   // 8 channels * 2 bytes
     static constexpr int kElemsPerWord = 2;
+    static constexpr bool kHalfPipe = true;    // float16 arithmetic needs few enough registers for 3 blocks per SM
     static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); }
     static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
     {
@@ -157,20 +166,22 @@ struct DT<__half> {
         x = f.x;
         y = f.y;
     }
-    static __device__ __forceinline__ void absdiff(float &a0, float &a1, uint32_t qw, uint32_t kw)
+    static __device__ __forceinline__ void absdiff(float &a0, float &, uint32_t qw, uint32_t kw)
     {
-        const __half2 d = __habs2(__hsub2(*reinterpret_cast<const __half2 *>(&qw), *reinterpret_cast<const __half2 *>(&kw)));
+        // the difference is rounded to float16 (as the reference does), its magnitude is added in float32
+        const __half2 d = __hsub2(*reinterpret_cast<const __half2 *>(&qw), *reinterpret_cast<const __half2 *>(&kw));
         const float2 f = __half22float2(d);
-        a0 += f.x;
-        a1 += f.y;
+        a0 += fabsf(f.x) + fabsf(f.y);
     }
     using Bcast = __half2;
     static __device__ __forceinline__ Bcast bcast(__half a) { return __half2half2(a); }
     static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o)
     {
-        const float2 f = __half22float2(__hmul2(a, *reinterpret_cast<const __half2 *>(&vw)));
-        o[0] += f.x;
-        o[1] += f.y;
+        // product rounded to float16, then added to the float32 sum by the mixed-precision add of sm_100
+        const __half2 pr = __hmul2_rn(a, *reinterpret_cast<const __half2 *>(&vw));
+        const uint32_t u = *reinterpret_cast<const uint32_t *>(&pr);
+        o[0] = add_f32_f16(o[0], static_cast<unsigned short>(u & 0xffffu));
+        o[1] = add_f32_f16(o[1], static_cast<unsigned short>(u >> 16));
     }
     static __device__ __forceinline__ uint32_t pack(const float *o)
     {
@@ -181,8 +192,9 @@ struct DT<__half> {
     static __device__ __forceinline__ A a_zero() { return __ushort_as_half(0); }
     static __device__ __forceinline__ A a_from(float x) { return __float2half_rn(x); }
     static __device__ __forceinline__ float a_to(A a) { return __half2float(a); }
-    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul(x, y); }
-    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd(x, y); }
+    // the _rn forms are never contracted into one fused multiply-add: the product must round on its own
+    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul_rn(x, y); }
+    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd_rn(x, y); }
     static __device__ __forceinline__ uint32_t a_pack(const A *a)
     {
         const __half2 t = __halves2half2(a[0], a[1]);
@@ -194,6 +206,7 @@ template <>
 struct DT<__nv_bfloat16> {
     static constexpr int kWordsPerChunk = 4;
     static constexpr int kElemsPerWord = 2;
+    static constexpr bool kHalfPipe = false;
     static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
     static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
     {
@@ -213,7 +226,7 @@ struct DT<__nv_bfloat16> {
     static __device__ __forceinline__ Bcast bcast(__nv_bfloat16 a) { return __bfloat162bfloat162(a); }
     static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o)
     {
-        const __nv_bfloat162 t = __hmul2(a, *reinterpret_cast<const __nv_bfloat162 *>(&vw));
+        const __nv_bfloat162 t = __hmul2_rn(a, *reinterpret_cast<const __nv_bfloat162 *>(&vw));
         const uint32_t u = *reinterpret_cast<const uint32_t *>(&t);
         o[0] += __uint_as_float(u << 16);
         o[1] += __uint_as_float(u & 0xffff0000u);
@@ -227,8 +240,9 @@ struct DT<__nv_bfloat16> {
     static __device__ __forceinline__ A a_zero() { return __ushort_as_bfloat16(0); }
     static __device__ __forceinline__ A a_from(float x) { return __float2bfloat16_rn(x); }
     static __device__ __forceinline__ float a_to(A a) { return __bfloat162float(a); }
-    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul(x, y); }
-    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd(x, y); }
+    // the _rn forms are never contracted into one fused multiply-add: the product must round on its own
+    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul_rn(x, y); }
+    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd_rn(x, y); }
     static __device__ __forceinline__ uint32_t a_pack(const A *a)
     {
         const __nv_bfloat162 t = __halves2bfloat162(a[0], a[1]);
@@ -237,6 +251,21 @@ struct DT<__nv_bfloat16> {
 };
 
 // ------------------------------------------------------------------ shared pieces
+
+// exp for the softmax.  expf() (2 ulp) is what eager PyTorch uses on the GPU; the
+// fast intrinsic is 2 + |1.2 x| ulp, which after rounding to 16 bits flips the
+// last bit of several per cent of the attention weights.
+#ifndef MATCHATTN_FAST_EXP
+#define MATCHATTN_FAST_EXP 0
+#endif
+__device__ __forceinline__ float softmax_exp(float x)
+{
+#if MATCHATTN_FAST_EXP
+    return __expf(x);
+#else
+    return expf(x);
+#endif
+}
 
 // Window origin: floor of the centre, limited to the range in which the
 // replicate clamp of the taps cannot tell the difference (keeps the int
@@ -265,7 +294,17 @@ __device__ __forceinline__ float finish_score(float l1, float scale)
     return DT<T>::rnd(DT<T>::rnd(-l1) * scale);
 }
 
-// BilinearSoftmax over a (2R+2)^2 score window held in registers.
+// BilinearSoftmax over a (2R+2)^2 score window held in registers: four shifted
+// (2R+1)^2 sub-windows, a softmax in each, blended by the bilinear weights in
+// the order nw, ne, sw, se with a rounding to T after every step.
+//
+// softmax(x)_m = exp(x_m - c) / sum exp(x - c) for any c, so the exponentials
+// are taken once per tap around the maximum of the whole window and shared by
+// the four sub-windows (their sums are built from shared row and column
+// partial sums).  If a sub-window's own maximum lies so far below the global
+// one that its exponentials could underflow, every sub-window is evaluated
+// around its own maximum instead.  Everything is unrolled with constant
+// indices so that the arrays stay in registers.
 template <typename T, int R>
 __device__ __forceinline__ void bilinear_softmax(const float (&s)[(2 * R + 2) * (2 * R + 2)], const float (&w)[4],
                                                  typename DT<T>::A (&a)[(2 * R + 2) * (2 * R + 2)])
@@ -274,41 +313,101 @@ __device__ __forceinline__ void bilinear_softmax(const float (&s)[(2 * R + 2) * 
     using A = typename DT<T>::A;
 #pragma unroll
     for (int m = 0; m < M; ++m) a[m] = DT<T>::a_zero();
+
+    // sub-window maxima from shared column / row partial maxima
+    float sub_max[4];
+    {
+        float top[SIDE], bot[SIDE];
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-        const int oy = t >> 1, ox = t & 1;
-        float mx = s[oy * SIDE + ox];
+        for (int i = 0; i < SIDE; ++i) {
+            float mid = s[SIDE + i];
 #pragma unroll
-        for (int j = 0; j < SUB; ++j)
+            for (int j = 2; j < SUB; ++j) mid = fmaxf(mid, s[j * SIDE + i]);
+            top[i] = fmaxf(s[i], mid);
+            bot[i] = fmaxf(mid, s[(SIDE - 1) * SIDE + i]);
+        }
+        float mt = top[1], mb = bot[1];
 #pragma unroll
-            for (int i = 0; i < SUB; ++i) mx = fmaxf(mx, s[(j + oy) * SIDE + i + ox]);
-        float e[SUB * SUB];
-        float den = 0.f;
+        for (int i = 2; i < SUB; ++i) {
+            mt = fmaxf(mt, top[i]);
+            mb = fmaxf(mb, bot[i]);
+        }
+        sub_max[0] = fmaxf(top[0], mt);
+        sub_max[1] = fmaxf(mt, top[SIDE - 1]);
+        sub_max[2] = fmaxf(bot[0], mb);
+        sub_max[3] = fmaxf(mb, bot[SIDE - 1]);
+    }
+    const float gmax = fmaxf(fmaxf(sub_max[0], sub_max[1]), fmaxf(sub_max[2], sub_max[3]));
+    const float gmin = fminf(fminf(sub_max[0], sub_max[1]), fminf(sub_max[2], sub_max[3]));
+
+    if (gmax - gmin < 60.f) {
+        float e[M];
 #pragma unroll
-        for (int j = 0; j < SUB; ++j)
+        for (int m = 0; m < M; ++m) e[m] = softmax_exp(s[m] - gmax);
+        float top[SIDE], bot[SIDE];
 #pragma unroll
-            for (int i = 0; i < SUB; ++i) {
-                const float ev = __expf(s[(j + oy) * SIDE + i + ox] - mx);
-                e[j * SUB + i] = ev;
-                den += ev;
-            }
-        const float inv = __frcp_rn(den);
-        const A wt = DT<T>::a_from(w[t]);
+        for (int i = 0; i < SIDE; ++i) {
+            float mid = e[SIDE + i];
 #pragma unroll
-        for (int j = 0; j < SUB; ++j)
+            for (int j = 2; j < SUB; ++j) mid += e[j * SIDE + i];
+            top[i] = e[i] + mid;
+            bot[i] = mid + e[(SIDE - 1) * SIDE + i];
+        }
+        float mt = top[1], mb = bot[1];
 #pragma unroll
-            for (int i = 0; i < SUB; ++i) {
-                const int m = (j + oy) * SIDE + i + ox;
-                const A p = DT<T>::a_from(e[j * SUB + i] * inv);
-                a[m] = DT<T>::a_add(a[m], DT<T>::a_mul(wt, p));
-            }
+        for (int i = 2; i < SUB; ++i) {
+            mt += top[i];
+            mb += bot[i];
+        }
+        const float den[4] = {top[0] + mt, mt + top[SIDE - 1], bot[0] + mb, mb + bot[SIDE - 1]};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int oy = t >> 1, ox = t & 1;
+            const float inv = __frcp_rn(den[t]);
+            const A wt = DT<T>::a_from(w[t]);
+#pragma unroll
+            for (int j = 0; j < SUB; ++j)
+#pragma unroll
+                for (int i = 0; i < SUB; ++i) {
+                    const int m = (j + oy) * SIDE + i + ox;
+                    a[m] = DT<T>::a_add(a[m], DT<T>::a_mul(wt, DT<T>::a_from(e[m] * inv)));
+                }
+        }
+    } else {   // rare: widely spread scores, or a NaN score
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int oy = t >> 1, ox = t & 1;
+            float den = 0.f;
+#pragma unroll
+            for (int j = 0; j < SUB; ++j)
+#pragma unroll
+                for (int i = 0; i < SUB; ++i) den += softmax_exp(s[(j + oy) * SIDE + i + ox] - sub_max[t]);
+            const float inv = __frcp_rn(den);
+            const A wt = DT<T>::a_from(w[t]);
+#pragma unroll
+            for (int j = 0; j < SUB; ++j)
+#pragma unroll
+                for (int i = 0; i < SUB; ++i) {
+                    const int m = (j + oy) * SIDE + i + ox;
+                    const A p = DT<T>::a_from(softmax_exp(s[m] - sub_max[t]) * inv);
+                    a[m] = DT<T>::a_add(a[m], DT<T>::a_mul(wt, p));
+                }
+        }
     }
 }
 
 // ------------------------------------------------------------------ the specialised kernel
 
+// resident blocks per SM the register allocation is held to (more warps hide the gather latency)
+template <typename T, int R, int CPL>
+constexpr int min_blocks()
+{
+    if (R != 1) return 1;
+    return (DT<T>::kHalfPipe && CPL <= 2) ? 3 : 2;
+}
+
 template <typename T, int R, int CPL, bool MULTI>
-__global__ void __launch_bounds__(kThreads) fused_forward_kernel(const Params p)
+__global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forward_kernel(const Params p)
 {
     constexpr int SIDE = 2 * R + 2, M = SIDE * SIDE;
     constexpr int NW = CPL * DT<T>::kWordsPerChunk;        // 32-bit words of K (or V, q, out) per lane and tap

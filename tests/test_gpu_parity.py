@@ -68,8 +68,9 @@ def test_kernel_matches_oracle(shape, dtype):
     scale = hd ** -0.5
     ref_out, ref_attn = _oracle().forward(*inputs, H, W, r, scale)
     out, attn = run_kernel(inputs, H, W, r, scale)
-    assert_close(attn, ref_attn, dtype, "attn")
-    assert_close(out, ref_out, dtype, "out")
+    ties = hd > 16          # see _cases.py: rounding ties of wide-head score sums
+    assert_close(attn, ref_attn, dtype, "attn", ties=ties)
+    assert_close(out, ref_out, dtype, "out", ties=ties)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
@@ -120,6 +121,7 @@ def test_properties_at_full_size():
     the same result as a per-head run, and shifting the whole problem by one token shifts the result."""
     B, H, W, h, hd, r = 2, 384, 384, 8, 16, 1
     mo, q, k, v = (t.cuda() for t in make_inputs(11, B, H, W, h, hd, r, torch.float32, kind="flow", border_frac=0.0))
+    mo = (mo * 64).round() / 64          # so that x + 1 below is exact and the fractions do not change
     ma = _ma()
     out, attn = ma.match_attention(mo, q, k, v, H, W, r, 0.25)
     assert (attn.sum(-1) - 1).abs().max().item() < 1e-5
