@@ -58,14 +58,17 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, MEASURED_PEAKS.json absent)"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries
+# (profiles/fused_forward_f16_cpl2_op_384x384_b1.md: 169.3 MB for the one-item case; traffic is
+# proportional to the items of a launch, so the four-item bench launch moves four times that)
+NCU_TRAFFIC_BYTES = {
+    "op_384x384_b1_h8x16_r1_f16_flow": 169.3e6,
+    "op_384x384_b4_h8x16_r1_f16_flow": 4 * 169.3e6,
+}
+
+
 def ncu_traffic_per_launch(workload):
-    """dram bytes read+written per launch from the committed ncu summary, if one exists."""
-    path = os.path.join(ROOT, "profiles", "traffic.json")
-    try:
-        with open(path) as f:
-            return json.load(f).get(workload)
-    except Exception:
-        return None
+    return NCU_TRAFFIC_BYTES.get(workload)
 
 
 class ClockSampler:
@@ -180,6 +183,71 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_band_mode(args, rank, local_rank, world):
+    """One very large pair split by query row bands (strong scaling): rank 0 owns q/k/v/max_offset,
+    K and V are broadcast over NCCL, every rank runs the kernel on its band, outputs return to rank 0."""
+    import torch.distributed as dist
+    import matchattention_b200 as ma
+    from matchattention_b200.band import band_match_attention, band_rows
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, H, W, h, hd, r, dtype = 2, 1024, 1024, 4, 32, 1, torch.float16      # a 4096x4096 pair at 1/4 resolution
+    N, C = H * W, h * hd
+    kv = [torch.empty(B, N, C, dtype=dtype, device=dev) for _ in range(2)]
+    full = (None, None, None, None)
+    if rank == 0:
+        g = torch.Generator(device=dev).manual_seed(99)
+        q, k, v = (torch.randn(B, N, C, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(3))
+        ys, xs = torch.meshgrid(torch.arange(H, device=dev, dtype=torch.float32),
+                                torch.arange(W, device=dev, dtype=torch.float32), indexing="ij")
+        # smooth flow of at most 32 tokens (128 px): low-resolution noise, bilinearly upsampled
+        coarse = (torch.rand(B, 2, 9, 9, generator=g, device=dev) * 2 - 1) * 32.0
+        flow = torch.nn.functional.interpolate(coarse, size=(H, W), mode="bilinear", align_corners=True)
+        mo = torch.stack((xs + flow[:, 0], ys + flow[:, 1]), dim=-1).view(B, N, 1, 2).expand(B, N, h, 2)
+        mo = torch.cat((mo[..., :1].clamp(r, W - 1 - r - 1e-3), mo[..., 1:].clamp(r, H - 1 - r - 1e-3)), -1)
+        full = (mo.to(dtype).contiguous(), q, k, v)
+
+    def step():
+        if world == 1:
+            return ma.match_attention(*full, H, W, r, hd ** -0.5)
+        return band_match_attention(*full, B, H, W, h, hd, r, hd ** -0.5, dtype, dev, kv_buffers=kv)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    if rank == 0:
+        line = {"metric": "matchattention_queries_per_s", "value": B * N / (ms_per_step * 1e-3), "unit": "queries/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": "op_1024x1024_b2_h4x32_r1_f16_rowband", "mode": "row bands, K/V broadcast",
+                           "kv_broadcast_bytes_per_step": 2 * B * N * C * 2, "band_rows": band_rows(H, world, 0)},
+                "gpu_launches": args.steps}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def config_dict(name, wl):
     return {"workload": name, "B_per_gpu": wl["B"], "token_map": [wl["H"], wl["W"]], "heads": wl["h"],
             "head_dim": wl["hd"], "win_r": wl["r"], "window_taps": (2 * wl["r"] + 2) ** 2,
@@ -195,6 +263,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--mode", choices=["pairs", "band"], default="pairs",
+                    help="pairs: every GPU its own batch (default); band: one large pair split by query row bands")
     ap.add_argument("--tile-w", type=int, default=0)
     ap.add_argument("--chunks-per-lane", type=int, default=0)
     args = ap.parse_args()
@@ -211,6 +281,9 @@ def main():
     import matchattention_b200 as ma   # raises if the CUDA library is missing
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    if args.mode == "band":
+        run_band_mode(args, rank, local_rank, world)
+        return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None

@@ -1,0 +1,65 @@
+"""CPU tests of the row-band multi-GPU path: world_size 2 and 3 over gloo.  The band
+computation is injected (the CPU oracle), so what is tested is the partition, the
+broadcast of K/V, the movement of the band inputs and the reassembly of the outputs."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_band_rows_partition():
+    from matchattention_b200.band import band_rows
+    for H in (1, 2, 7, 96, 1024, 1025):
+        for world in (1, 2, 3, 4, 8):
+            bands = [band_rows(H, world, p) for p in range(world)]
+            assert bands[0][0] == 0 and bands[-1][1] == H
+            assert all(bands[i][1] == bands[i + 1][0] for i in range(world - 1))
+            sizes = [b - a for a, b in bands]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def _worker(rank, world, port, H, W, results):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from _cases import make_inputs
+        from matchattention_b200.band import band_match_attention
+        B, h, hd, r = 2, 2, 8, 1
+        mo, q, k, v = make_inputs(31, B, H, W, h, hd, r, torch.float16, kind="flow", spread=4.0)
+
+        def op(mo_b, q_b, kk, vv, H_, W_, r_, scale, r0, r1, need_attn):
+            return oracle.forward(mo_b, q_b, kk, vv, H_, W_, r_, scale, q_row_begin=r0, q_row_end=r1, nthreads=1,
+                                  want_attn=need_attn)
+
+        args = (mo, q, k, v) if rank == 0 else (None, None, None, None)
+        out, attn = band_match_attention(*args, B, H, W, h, hd, r, 0.3, torch.float16, torch.device("cpu"), op=op)
+        if rank == 0:
+            ref_out, ref_attn = oracle.forward(mo, q, k, v, H, W, r, 0.3, nthreads=1)
+            results.put((bool(torch.equal(out, ref_out)), bool(torch.equal(attn, ref_attn))))
+        else:
+            assert out is None and attn is None
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,H", [(2, 10), (3, 10), (5, 4)])
+def test_band_split_reassembles_the_full_result(world, H):
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = 29500 + (os.getpid() + world * 7 + H) % 2000
+    procs = [ctx.Process(target=_worker, args=(rank, world, port, H, 8, results)) for rank in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert results.get(timeout=5) == (True, True)

@@ -1,0 +1,53 @@
+"""GPU test of the row-band path over NCCL: needs at least two GPUs (skipped otherwise).
+Each rank is its own process on its own GPU; the result on rank 0 must equal the
+single-GPU result bit for bit and match the oracle."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, results):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from _cases import make_inputs
+        from matchattention_b200 import match_attention
+        from matchattention_b200.band import band_match_attention
+        B, H, W, h, hd, r = 2, 61, 40, 4, 32, 1
+        args = (None, None, None, None)
+        if rank == 0:
+            args = tuple(t.to(dev) for t in make_inputs(41, B, H, W, h, hd, r, torch.float16, kind="flow", spread=9.0))
+        out, attn = band_match_attention(*args, B, H, W, h, hd, r, 0.2, torch.float16, dev)
+        torch.cuda.synchronize()
+        if rank == 0:
+            one_out, one_attn = match_attention(*args, H, W, r, 0.2)
+            results.put((bool(torch.equal(out, one_out)), bool(torch.equal(attn, one_attn))))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_band_split_over_nccl_equals_single_gpu():
+    world = min(torch.cuda.device_count(), 4)
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = 29600 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(rank, world, port, results)) for rank in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    assert results.get(timeout=5) == (True, True)
