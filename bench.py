@@ -267,6 +267,7 @@ def main():
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands")
     ap.add_argument("--tile-w", type=int, default=0)
     ap.add_argument("--chunks-per-lane", type=int, default=0)
+    ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 scalar kernel, 2 matrix-instruction kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -298,7 +299,7 @@ def main():
     mo, q, k, v = (t.to(dev) for t in host)
     out = torch.empty_like(q)
     attn = q.new_empty(B, H * W, h, M)
-    knobs = dict(tile_w=args.tile_w, chunks_per_lane=args.chunks_per_lane)
+    knobs = dict(tile_w=args.tile_w, chunks_per_lane=args.chunks_per_lane, variant=args.variant)
 
     def step():
         ma.launch(mo, q, k, v, out, attn, H, W, (r, r), "l1_norm", wl["scale"], **knobs)

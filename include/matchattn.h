@@ -51,6 +51,7 @@ extern "C" {
 #define MATCHATTN_ERR_WINDOW         6  /* rx != ry, r < 0 or r above the supported maximum    */
 #define MATCHATTN_ERR_ALIGN          7  /* a pointer is not aligned to its element size       */
 #define MATCHATTN_ERR_TOO_LARGE      8  /* sizes overflow the 32-bit index ranges in use      */
+#define MATCHATTN_ERR_VARIANT        9  /* the kernel variant asked for does not cover the arguments */
 #define MATCHATTN_ERR_CUDA         100  /* 100 + cudaError_t of a failed launch               */
 
 /* largest window radius accepted */
@@ -92,7 +93,10 @@ MATCHATTN_API int matchattn_fused_forward(const void *max_offset, const void *q,
  *                 specialised one exists (used by the tests to cover it);
  *   chunks_per_lane  how many 8-channel chunks of a head one lane owns (0 =
  *                 choose automatically; a value that does not divide hd/8 into a
- *                 power-of-two number of lanes falls back to the any-shape kernel).
+ *                 power-of-two number of lanes falls back to the any-shape kernel);
+ *   variant       0 = choose automatically; 1 = the scalar kernel (float32 sums on the
+ *                 CUDA cores); 2 = the kernel that sums with warp matrix instructions
+ *                 (16-bit types, r = 1, head width <= 40; MATCHATTN_ERR_VARIANT otherwise).
  * No counterpart in the reference.
  */
 MATCHATTN_API int matchattn_fused_forward_ex(const void *max_offset, const void *q, const void *k, const void *v,
@@ -100,7 +104,7 @@ MATCHATTN_API int matchattn_fused_forward_ex(const void *max_offset, const void 
                                int B, int H, int W, int h, int hd, int rx, int ry,
                                int dtype, int attn_type, float scale,
                                int q_row_begin, int q_row_end, void *cuda_stream,
-                               int tile_w, int force_generic, int chunks_per_lane);
+                               int tile_w, int force_generic, int chunks_per_lane, int variant);
 
 /* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */

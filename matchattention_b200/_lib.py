@@ -31,7 +31,7 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_fused_forward.restype = _i
     lib.matchattn_fused_forward.argtypes = base
     lib.matchattn_fused_forward_ex.restype = _i
-    lib.matchattn_fused_forward_ex.argtypes = base + [_i, _i, _i]
+    lib.matchattn_fused_forward_ex.argtypes = base + [_i, _i, _i, _i]
     lib.matchattn_describe_dispatch.restype = ctypes.c_char_p
     lib.matchattn_describe_dispatch.argtypes = [_i] * 5
     lib.matchattn_version.restype = _i

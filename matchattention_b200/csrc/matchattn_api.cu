@@ -6,6 +6,7 @@
 #include <stdio.h>
 
 #include "matchattn_kernels.cuh"
+#include "matchattn_mma.cuh"
 
 namespace matchattn {
 namespace {
@@ -14,7 +15,11 @@ struct Plan {
     bool fast;
     int cpl;   // chunks (8 channels) per lane
     int lph;   // lanes per head
+    bool mma;  // 16-bit, one lane per head, r == 1: accumulate with matrix instructions
 };
+
+constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2;
+constexpr int kMmaItemsPerBlock = 1024;   // 8 warps x 128 items
 
 inline bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 inline int ilog2(int v)
@@ -29,7 +34,7 @@ inline int ilog2(int v)
 // odd == 5), and the remaining power of two becomes lanes per head.
 Plan make_plan(int h, int hd, int r, int cpl_request)
 {
-    Plan pl{false, 0, 0};
+    Plan pl{false, 0, 0, false};
     if (hd % 8 != 0 || (r != 1 && r != 2)) return pl;
     const int hd8 = hd / 8;
     int odd = hd8;
@@ -53,6 +58,13 @@ Plan make_plan(int h, int hd, int r, int cpl_request)
 inline bool aligned(const void *p, uintptr_t a) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 template <typename T>
+cudaError_t launch_mma_if_16bit(const Params &p, int r, int cpl, dim3 grid, cudaStream_t stream)
+{
+    if constexpr (sizeof(T) == 2) return launch_mma<T>(p, r, cpl, grid, stream);
+    else return cudaErrorInvalidValue;
+}
+
+template <typename T>
 int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t stream)
 {
     cudaError_t err;
@@ -60,7 +72,8 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
         p.lph = pl.lph;
         p.lph_shift = ilog2(pl.lph);
         p.G = p.h * pl.lph;
-        const int qpb = kThreads / p.G;              // queries per block (>= 1)
+        const int lanes_per_block = pl.mma ? kMmaItemsPerBlock : kThreads;
+        const int qpb = lanes_per_block / p.G;       // queries per block (>= 1)
         const int qpw = p.G >= 32 ? 1 : 32 / p.G;    // queries a warp covers, kept in one row
         int tw;
         if (tile_w_request > 0) {
@@ -80,7 +93,9 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
         const int tiles_y = (p.rows + p.tile_h - 1) / p.tile_h;
         const long long blocks = 1LL * p.tiles_x * tiles_y;
         if (blocks > 2147483647LL) return MATCHATTN_ERR_TOO_LARGE;
-        err = launch_fast<T>(p, r, pl.cpl, pl.lph > 1, dim3(static_cast<unsigned>(blocks), p.B), stream);
+        const dim3 grid(static_cast<unsigned>(blocks), p.B);
+        err = pl.mma ? launch_mma_if_16bit<T>(p, r, pl.cpl, grid, stream)
+                     : launch_fast<T>(p, r, pl.cpl, pl.lph > 1, grid, stream);
     } else {
         const long long per_item = 1LL * p.Nq * p.h;
         const long long blocks = (per_item + kThreads - 1) / kThreads;
@@ -92,7 +107,8 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
 
 int forward_impl(const void *max_offset, const void *q, const void *k, const void *v, void *out, void *attn_out,
                  int B, int H, int W, int h, int hd, int rx, int ry, int dtype, int attn_type, float scale,
-                 int q_row_begin, int q_row_end, void *cuda_stream, int tile_w, int force_generic, int cpl_request)
+                 int q_row_begin, int q_row_end, void *cuda_stream, int tile_w, int force_generic, int cpl_request,
+                 int variant)
 {
     if (!max_offset || !q || !k || !v || !out) return MATCHATTN_ERR_NULL;
     if (dtype != MATCHATTN_F32 && dtype != MATCHATTN_F16 && dtype != MATCHATTN_BF16) return MATCHATTN_ERR_DTYPE;
@@ -111,7 +127,7 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
         !aligned(out, esize) || !aligned(attn_out, esize))
         return MATCHATTN_ERR_ALIGN;
 
-    Plan pl = force_generic ? Plan{false, 0, 0} : make_plan(h, hd, r, cpl_request);
+    Plan pl = force_generic ? Plan{false, 0, 0, false} : make_plan(h, hd, r, cpl_request);
     if (pl.fast) {
         // vector width of a lane's slice decides the alignment the specialised kernel needs
         const int slice_bytes = pl.cpl * 8 * static_cast<int>(esize);
@@ -120,6 +136,15 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
         if (!aligned(q, need) || !aligned(k, need) || !aligned(v, need) || !aligned(out, need) ||
             !aligned(attn_out, need_attn))
             pl.fast = false;
+    }
+    if (pl.fast) {
+        const bool mma_ok = esize == 2 && r == 1 && pl.lph == 1 && h <= kMmaItemsPerBlock;
+        // the direct-gather form of the matrix-instruction kernel runs at one block per SM and is
+        // latency-bound; it is selected only on request
+        pl.mma = mma_ok && variant == kVariantMma;
+        if (variant == kVariantMma && !mma_ok) return MATCHATTN_ERR_VARIANT;
+    } else if (variant == kVariantMma) {
+        return MATCHATTN_ERR_VARIANT;
     }
 
     Params p{};
@@ -148,17 +173,17 @@ int matchattn_fused_forward(const void *max_offset, const void *q, const void *k
                             int attn_type, float scale, int q_row_begin, int q_row_end, void *cuda_stream)
 {
     return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
-                                   scale, q_row_begin, q_row_end, cuda_stream, 0, 0, 0);
+                                   scale, q_row_begin, q_row_end, cuda_stream, 0, 0, 0, 0);
 }
 
 int matchattn_fused_forward_ex(const void *max_offset, const void *q, const void *k, const void *v, void *out,
                                void *attn_out, int B, int H, int W, int h, int hd, int rx, int ry, int dtype,
                                int attn_type, float scale, int q_row_begin, int q_row_end, void *cuda_stream,
-                               int tile_w, int force_generic, int chunks_per_lane)
+                               int tile_w, int force_generic, int chunks_per_lane, int variant)
 {
     return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
                                    scale, q_row_begin, q_row_end, cuda_stream, tile_w, force_generic,
-                                   chunks_per_lane);
+                                   chunks_per_lane, variant);
 }
 
 const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned)
@@ -190,6 +215,7 @@ const char *matchattn_strerror(int status)
     case MATCHATTN_ERR_WINDOW: return "unsupported window: rx must equal ry and 0 <= r <= 4";
     case MATCHATTN_ERR_ALIGN: return "a pointer is not aligned to its element size";
     case MATCHATTN_ERR_TOO_LARGE: return "sizes exceed the supported index range";
+    case MATCHATTN_ERR_VARIANT: return "the requested kernel variant does not cover these arguments";
     default: break;
     }
     if (status >= MATCHATTN_ERR_CUDA) return cudaGetErrorString(static_cast<cudaError_t>(status - MATCHATTN_ERR_CUDA));

@@ -144,13 +144,12 @@ struct DT<float> {
     // o += a * v over the elements of one word (o points at this word's accumulators)
     static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o) { o[0] = fmaf(a, __uint_as_float(vw), o[0]); }
     static __device__ __forceinline__ uint32_t pack(const float *o) { return __float_as_uint(o[0]); }
-    using A = float;  // storage type of the attention weights
-    static __device__ __forceinline__ A a_zero() { return 0.f; }
-    static __device__ __forceinline__ A a_from(float x) { return x; }
-    static __device__ __forceinline__ float a_to(A a) { return a; }
-    static __device__ __forceinline__ A a_mul(A x, A y) { return x * y; }
-    static __device__ __forceinline__ A a_add(A x, A y) { return x + y; }
-    static __device__ __forceinline__ uint32_t a_pack(const A *a) { return __float_as_uint(a[0]); }
+    // attention weights live in 32-bit words holding kElemsPerWord of them ("lo" element first)
+    static __device__ __forceinline__ uint32_t aw_from(float lo, float) { return __float_as_uint(lo); }
+    static __device__ __forceinline__ uint32_t aw_bcast(float w) { return __float_as_uint(w); }
+    static __device__ __forceinline__ uint32_t aw_mul(uint32_t x, uint32_t y) { return __float_as_uint(__fmul_rn(__uint_as_float(x), __uint_as_float(y))); }
+    static __device__ __forceinline__ uint32_t aw_add(uint32_t x, uint32_t y) { return __float_as_uint(__fadd_rn(__uint_as_float(x), __uint_as_float(y))); }
+    static __device__ __forceinline__ Bcast aw_tap(const uint32_t *aw, int m) { return __uint_as_float(aw[m]); }
 };
 
 template <>
@@ -188,17 +187,32 @@ struct DT<__half> {
         const __half2 t = __floats2half2_rn(o[0], o[1]);
         return *reinterpret_cast<const uint32_t *>(&t);
     }
-    using A = __half;
-    static __device__ __forceinline__ A a_zero() { return __ushort_as_half(0); }
-    static __device__ __forceinline__ A a_from(float x) { return __float2half_rn(x); }
-    static __device__ __forceinline__ float a_to(A a) { return __half2float(a); }
-    // the _rn forms are never contracted into one fused multiply-add: the product must round on its own
-    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul_rn(x, y); }
-    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd_rn(x, y); }
-    static __device__ __forceinline__ uint32_t a_pack(const A *a)
+    static __device__ __forceinline__ float unpack(uint32_t w, int hi)
     {
-        const __half2 t = __halves2half2(a[0], a[1]);
+        const __half2 t = *reinterpret_cast<const __half2 *>(&w);
+        return hi ? __high2float(t) : __low2float(t);
+    }
+    static __device__ __forceinline__ uint32_t aw_from(float lo, float hi)
+    {
+        const __half2 t = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    static __device__ __forceinline__ uint32_t aw_bcast(float w) { return aw_from(w, w); }
+    // the _rn forms are never contracted into a fused multiply-add: the product must round on its own
+    static __device__ __forceinline__ uint32_t aw_mul(uint32_t x, uint32_t y)
+    {
+        const __half2 t = __hmul2_rn(*reinterpret_cast<const __half2 *>(&x), *reinterpret_cast<const __half2 *>(&y));
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    static __device__ __forceinline__ uint32_t aw_add(uint32_t x, uint32_t y)
+    {
+        const __half2 t = __hadd2_rn(*reinterpret_cast<const __half2 *>(&x), *reinterpret_cast<const __half2 *>(&y));
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    static __device__ __forceinline__ Bcast aw_tap(const uint32_t *aw, int m)
+    {
+        const uint32_t u = (m & 1) ? __byte_perm(aw[m >> 1], 0, 0x3232) : __byte_perm(aw[m >> 1], 0, 0x1010);
+        return *reinterpret_cast<const __half2 *>(&u);
     }
 };
 
@@ -236,17 +250,32 @@ struct DT<__nv_bfloat16> {
         const __nv_bfloat162 t = __floats2bfloat162_rn(o[0], o[1]);
         return *reinterpret_cast<const uint32_t *>(&t);
     }
-    using A = __nv_bfloat16;
-    static __device__ __forceinline__ A a_zero() { return __ushort_as_bfloat16(0); }
-    static __device__ __forceinline__ A a_from(float x) { return __float2bfloat16_rn(x); }
-    static __device__ __forceinline__ float a_to(A a) { return __bfloat162float(a); }
-    // the _rn forms are never contracted into one fused multiply-add: the product must round on its own
-    static __device__ __forceinline__ A a_mul(A x, A y) { return __hmul_rn(x, y); }
-    static __device__ __forceinline__ A a_add(A x, A y) { return __hadd_rn(x, y); }
-    static __device__ __forceinline__ uint32_t a_pack(const A *a)
+    static __device__ __forceinline__ float unpack(uint32_t w, int hi)
     {
-        const __nv_bfloat162 t = __halves2bfloat162(a[0], a[1]);
+        return __uint_as_float(hi ? (w & 0xffff0000u) : (w << 16));
+    }
+    static __device__ __forceinline__ uint32_t aw_from(float lo, float hi)
+    {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    static __device__ __forceinline__ uint32_t aw_bcast(float w) { return aw_from(w, w); }
+    static __device__ __forceinline__ uint32_t aw_mul(uint32_t x, uint32_t y)
+    {
+        const __nv_bfloat162 t = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162 *>(&x),
+                                            *reinterpret_cast<const __nv_bfloat162 *>(&y));
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    static __device__ __forceinline__ uint32_t aw_add(uint32_t x, uint32_t y)
+    {
+        const __nv_bfloat162 t = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162 *>(&x),
+                                            *reinterpret_cast<const __nv_bfloat162 *>(&y));
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
+    static __device__ __forceinline__ Bcast aw_tap(const uint32_t *aw, int m)
+    {
+        const uint32_t u = (m & 1) ? __byte_perm(aw[m >> 1], 0, 0x3232) : __byte_perm(aw[m >> 1], 0, 0x1010);
+        return *reinterpret_cast<const __nv_bfloat162 *>(&u);
     }
 };
 
@@ -266,6 +295,7 @@ __device__ __forceinline__ float softmax_exp(float x)
     return expf(x);
 #endif
 }
+__device__ __forceinline__ float softmax_rcp(float x) { return __frcp_rn(x); }
 
 // Window origin: floor of the centre, limited to the range in which the
 // replicate clamp of the taps cannot tell the difference (keeps the int
@@ -305,14 +335,41 @@ __device__ __forceinline__ float finish_score(float l1, float scale)
 // one that its exponentials could underflow, every sub-window is evaluated
 // around its own maximum instead.  Everything is unrolled with constant
 // indices so that the arrays stay in registers.
+//
+// The result is written as 32-bit words `aw` holding kElemsPerWord consecutive
+// taps each, which is the layout of attn_out; in the 16-bit types the rounding
+// chain p -> w*p -> a + w*p runs on such pairs (a column that a sub-window does
+// not cover contributes w * 0 = +0, which leaves the sum unchanged).
+template <typename T, int R, typename ExpMinus>
+__device__ __forceinline__ void blend_subwindow(uint32_t (&aw)[(2 * R + 2) * (2 * R + 2) / DT<T>::kElemsPerWord],
+                                                const int t, const float wt, const float inv, ExpMinus e_of)
+{
+    constexpr int SIDE = 2 * R + 2, SUB = 2 * R + 1, EPW = DT<T>::kElemsPerWord;
+    const int oy = t >> 1, ox = t & 1;
+    const uint32_t wt_w = DT<T>::aw_bcast(wt);
+#pragma unroll
+    for (int j = 0; j < SUB; ++j)
+#pragma unroll
+        for (int iw = 0; iw < SIDE / EPW; ++iw) {
+            const int i0 = iw * EPW, i1 = i0 + EPW - 1;          // columns of this word
+            const bool in0 = i0 >= ox && i0 < ox + SUB, in1 = i1 >= ox && i1 < ox + SUB;
+            if (!in0 && !in1) continue;
+            const int m0 = (j + oy) * SIDE + i0;
+            const float p0 = in0 ? e_of(m0) * inv : 0.f;
+            const float p1 = (EPW == 2 && in1) ? e_of(m0 + 1) * inv : 0.f;
+            uint32_t &dst = aw[m0 / EPW];
+            dst = DT<T>::aw_add(dst, DT<T>::aw_mul(wt_w, DT<T>::aw_from(p0, p1)));
+        }
+}
+
 template <typename T, int R>
 __device__ __forceinline__ void bilinear_softmax(const float (&s)[(2 * R + 2) * (2 * R + 2)], const float (&w)[4],
-                                                 typename DT<T>::A (&a)[(2 * R + 2) * (2 * R + 2)])
+                                                 uint32_t (&aw)[(2 * R + 2) * (2 * R + 2) / DT<T>::kElemsPerWord])
 {
-    constexpr int SIDE = 2 * R + 2, SUB = 2 * R + 1, M = SIDE * SIDE;
-    using A = typename DT<T>::A;
+    constexpr int SIDE = 2 * R + 2, SUB = 2 * R + 1, M = SIDE * SIDE, EPW = DT<T>::kElemsPerWord;
+    static_assert(SIDE % EPW == 0, "a word never straddles two window rows");
 #pragma unroll
-    for (int m = 0; m < M; ++m) a[m] = DT<T>::a_zero();
+    for (int m = 0; m < M / EPW; ++m) aw[m] = 0u;
 
     // sub-window maxima from shared column / row partial maxima
     float sub_max[4];
@@ -361,37 +418,19 @@ __device__ __forceinline__ void bilinear_softmax(const float (&s)[(2 * R + 2) * 
         }
         const float den[4] = {top[0] + mt, mt + top[SIDE - 1], bot[0] + mb, mb + bot[SIDE - 1]};
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const int oy = t >> 1, ox = t & 1;
-            const float inv = __frcp_rn(den[t]);
-            const A wt = DT<T>::a_from(w[t]);
-#pragma unroll
-            for (int j = 0; j < SUB; ++j)
-#pragma unroll
-                for (int i = 0; i < SUB; ++i) {
-                    const int m = (j + oy) * SIDE + i + ox;
-                    a[m] = DT<T>::a_add(a[m], DT<T>::a_mul(wt, DT<T>::a_from(e[m] * inv)));
-                }
-        }
+        for (int t = 0; t < 4; ++t)
+            blend_subwindow<T, R>(aw, t, w[t], softmax_rcp(den[t]), [&](int m) { return e[m]; });
     } else {   // rare: widely spread scores, or a NaN score
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             const int oy = t >> 1, ox = t & 1;
+            const float mx = sub_max[t];
             float den = 0.f;
 #pragma unroll
             for (int j = 0; j < SUB; ++j)
 #pragma unroll
-                for (int i = 0; i < SUB; ++i) den += softmax_exp(s[(j + oy) * SIDE + i + ox] - sub_max[t]);
-            const float inv = __frcp_rn(den);
-            const A wt = DT<T>::a_from(w[t]);
-#pragma unroll
-            for (int j = 0; j < SUB; ++j)
-#pragma unroll
-                for (int i = 0; i < SUB; ++i) {
-                    const int m = (j + oy) * SIDE + i + ox;
-                    const A p = DT<T>::a_from(softmax_exp(s[m] - sub_max[t]) * inv);
-                    a[m] = DT<T>::a_add(a[m], DT<T>::a_mul(wt, p));
-                }
+                for (int i = 0; i < SUB; ++i) den += softmax_exp(s[(j + oy) * SIDE + i + ox] - mx);
+            blend_subwindow<T, R>(aw, t, w[t], softmax_rcp(den), [&](int m) { return softmax_exp(s[m] - mx); });
         }
     }
 }
@@ -413,7 +452,6 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     constexpr int NW = CPL * DT<T>::kWordsPerChunk;        // 32-bit words of K (or V, q, out) per lane and tap
     constexpr int EPW = DT<T>::kElemsPerWord;
     constexpr int SLICE = CPL * 8;                          // channels per lane
-    using A = typename DT<T>::A;
 
     // lane -> (query of the tile, head, slice of the head)
     const int tid = threadIdx.x;
@@ -485,16 +523,11 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
             s[j * SIDE + i] = finish_score<T>(part, p.scale);
         }
 
-    A a[M];
-    bilinear_softmax<T, R>(s, wgt, a);
+    constexpr int NWA = M / EPW;
+    uint32_t aw[NWA];
+    bilinear_softmax<T, R>(s, wgt, aw);
 
-    if (p.attn != nullptr && sl == 0 && valid) {
-        constexpr int NWA = M / EPW;
-        uint32_t aw[NWA];
-#pragma unroll
-        for (int w = 0; w < NWA; ++w) aw[w] = DT<T>::a_pack(&a[w * EPW]);
-        store_words<NWA>(static_cast<T *>(p.attn) + (bq * p.h + head) * M, aw);
-    }
+    if (p.attn != nullptr && sl == 0 && valid) store_words<NWA>(static_cast<T *>(p.attn) + (bq * p.h + head) * M, aw);
 
     // weighted sum of the value taps
     float o[NW * EPW];
@@ -506,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
         for (int i = 0; i < SIDE; ++i) {
             uint32_t vw[NW];
             load_words<NW>(vw, vb + (row[j] + col[i]));
-            const typename DT<T>::Bcast am = DT<T>::bcast(a[j * SIDE + i]);
+            const typename DT<T>::Bcast am = DT<T>::aw_tap(aw, j * SIDE + i);
 #pragma unroll
             for (int w = 0; w < NW; ++w) DT<T>::wmul(am, vw[w], &o[w * EPW]);
         }

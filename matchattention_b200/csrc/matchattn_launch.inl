@@ -1,6 +1,9 @@
 // Included once per element type with MATCHATTN_T defined: instantiates the
 // specialised kernels for that type and the switch that picks one.
 #include "matchattn_kernels.cuh"
+#ifdef MATCHATTN_T_IS_16BIT
+#include "matchattn_mma.cuh"
+#endif
 
 namespace matchattn {
 
@@ -28,6 +31,22 @@ cudaError_t launch_fast<MATCHATTN_T>(const Params &p, int r, int cpl, bool multi
     if (r == 2) return launch_fast_r<MATCHATTN_T, 2>(p, cpl, multi, grid, stream);
     return cudaErrorInvalidValue;
 }
+
+#ifdef MATCHATTN_T_IS_16BIT
+template <>
+cudaError_t launch_mma<MATCHATTN_T>(const Params &p, int r, int cpl, dim3 grid, cudaStream_t stream)
+{
+    if (r != 1) return cudaErrorInvalidValue;
+#define MA_CASE(CPL_)                                                                      \
+    if (cpl == CPL_) {                                                                     \
+        fused_forward_mma_kernel<MATCHATTN_T, 1, CPL_><<<grid, kThreads, 0, stream>>>(p);  \
+        return cudaGetLastError();                                                         \
+    }
+    MA_CASE(1) MA_CASE(2) MA_CASE(3) MA_CASE(4) MA_CASE(5)
+#undef MA_CASE
+    return cudaErrorInvalidValue;
+}
+#endif
 
 template <>
 cudaError_t launch_generic<MATCHATTN_T>(const Params &p, dim3 grid, cudaStream_t stream)

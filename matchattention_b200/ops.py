@@ -68,7 +68,7 @@ def _check_tensors(max_offset, q, k, v, output, attn_out, H, W, rows, attn_num):
 
 def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_type: str = "l1_norm",
            scale: float = 1.0, q_row_begin: int = 0, q_row_end: Optional[int] = None, *,
-           tile_w: int = 0, force_generic: bool = False, chunks_per_lane: int = 0) -> None:
+           tile_w: int = 0, force_generic: bool = False, chunks_per_lane: int = 0, variant: int = 0) -> None:
     """Validate, then enqueue the fused kernel on the current stream of q's device.
 
     ``attn_out`` may be None (the attention weights are then not written).  With
@@ -87,7 +87,7 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
             max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
             attn_out.data_ptr() if attn_out is not None else None,
             B, H, W, h, hd, rx, ry, _DTYPE_CODE[q.dtype], _lib.L1_NORM, float(scale),
-            q_row_begin, q_row_end, stream, int(tile_w), int(bool(force_generic)), int(chunks_per_lane))
+            q_row_begin, q_row_end, stream, int(tile_w), int(bool(force_generic)), int(chunks_per_lane), int(variant))
     _lib.check(status)
 
 
