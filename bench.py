@@ -268,6 +268,7 @@ def main():
     ap.add_argument("--tile-w", type=int, default=0)
     ap.add_argument("--chunks-per-lane", type=int, default=0)
     ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 scalar kernel, 2 matrix-instruction kernel")
+    ap.add_argument("--strategy", type=int, default=0, help="0 auto, 1 direct kernel, 2 binned path")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -299,7 +300,8 @@ def main():
     mo, q, k, v = (t.to(dev) for t in host)
     out = torch.empty_like(q)
     attn = q.new_empty(B, H * W, h, M)
-    knobs = dict(tile_w=args.tile_w, chunks_per_lane=args.chunks_per_lane, variant=args.variant)
+    knobs = dict(tile_w=args.tile_w, chunks_per_lane=args.chunks_per_lane, variant=args.variant,
+                 strategy=args.strategy)
 
     def step():
         ma.launch(mo, q, k, v, out, attn, H, W, (r, r), "l1_norm", wl["scale"], **knobs)

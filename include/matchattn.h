@@ -21,6 +21,8 @@
 #ifndef MATCHATTN_H_
 #define MATCHATTN_H_
 
+#include <stddef.h>
+
 #if defined(__GNUC__)
 #define MATCHATTN_API __attribute__((visibility("default")))
 #else
@@ -105,6 +107,36 @@ MATCHATTN_API int matchattn_fused_forward_ex(const void *max_offset, const void 
                                int dtype, int attn_type, float scale,
                                int q_row_begin, int q_row_end, void *cuda_stream,
                                int tile_w, int force_generic, int chunks_per_lane, int variant);
+
+/*
+ * The same operator with scratch memory from the caller, which opens the binned
+ * path: the queries are counting-sorted by the tile of the token map their window
+ * falls into and each tile of K/V is staged in shared memory once for all the
+ * queries that look at it.  It pays when sampling centres are spread widely
+ * (neighbouring queries then share no taps and the direct kernel is bound by
+ * L2 bandwidth).  Covered: float16 / bfloat16, r = 1, head width <= 40, one
+ * sampling centre per query shared by all heads; a call whose heads differ is
+ * detected on the device and served by the direct kernel in the same call.
+ *
+ *   workspace        device scratch of at least matchattn_workspace_bytes(...) bytes,
+ *                    256-byte aligned; contents need not be preserved between calls,
+ *                    but two calls that overlap on the device must not share it;
+ *   strategy         0 = let the library choose (currently always the direct kernel);
+ *                    1 = direct kernel (workspace may be NULL);
+ *                    2 = binned path, or MATCHATTN_ERR_VARIANT when it does not apply.
+ * Still allocates nothing and does not synchronise.  No counterpart in the reference
+ * (its driver allocates its own temporaries, models/src/match_former_fused_forward.cu:492-508).
+ */
+MATCHATTN_API int matchattn_fused_forward_ws(const void *max_offset, const void *q, const void *k, const void *v,
+                                             void *out, void *attn_out,
+                                             int B, int H, int W, int h, int hd, int rx, int ry,
+                                             int dtype, int attn_type, float scale,
+                                             int q_row_begin, int q_row_end, void *cuda_stream,
+                                             void *workspace, size_t workspace_bytes, int strategy);
+
+/* Scratch bytes the binned path needs for these sizes; 0 when it does not apply. */
+MATCHATTN_API size_t matchattn_workspace_bytes(int B, int H, int W, int h, int hd, int r, int dtype,
+                                               int q_row_begin, int q_row_end);
 
 /* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */

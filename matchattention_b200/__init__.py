@@ -9,18 +9,28 @@ Public surface:
   implementation so that the unmodified reference model runs on it with
   ``--mat_impl cuda``.
 
-Importing the package loads matchattention_b200/lib/libmatchattn_b200.so and
-fails if it has not been built (``python -m matchattention_b200.build``).
+The first use of any of these loads matchattention_b200/lib/libmatchattn_b200.so
+and raises if it has not been built (``python -m matchattention_b200.build``);
+there is no CPU or PyTorch fallback.  (The load is deferred to first use only so
+that the build module itself can be run from a tree without the library.)
 """
-from . import _lib
-from .ops import (MF_FusedForwardOps, describe_dispatch, fused_forward, fused_forward_ops, launch,
-                  match_attention)
+import importlib
 
-__all__ = ["MF_FusedForwardOps", "fused_forward", "fused_forward_ops", "match_attention", "launch",
-           "describe_dispatch", "install_dropin", "abi_version"]
+_OPS = ("MF_FusedForwardOps", "describe_dispatch", "fused_forward", "fused_forward_ops", "launch",
+        "match_attention", "workspace_bytes")
+__all__ = list(_OPS) + ["install_dropin", "abi_version"]
+
+
+def __getattr__(name):
+    if name in _OPS:
+        return getattr(importlib.import_module(".ops", __name__), name)
+    if name in ("ops", "_lib", "band", "build"):
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
 def abi_version() -> int:
+    from . import _lib
     return int(_lib.lib.matchattn_version())
 
 

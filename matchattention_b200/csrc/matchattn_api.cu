@@ -7,6 +7,7 @@
 
 #include "matchattn_kernels.cuh"
 #include "matchattn_mma.cuh"
+#include "matchattn_binned.cuh"
 
 namespace matchattn {
 namespace {
@@ -19,6 +20,46 @@ struct Plan {
 };
 
 constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2;
+constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2;
+constexpr long long kBinnedMinQueries = 32768;   // below this the three sorting passes cost more than they save
+
+// Geometry of the binned path; valid == false when the arguments are outside what it covers.
+struct BinGeometry {
+    bool valid;
+    int TX, TY, RW, RH, bins_x, bins_y, nbins, region_bytes;
+    size_t off_counts, off_ctrl, off_starts, off_cursors, off_bin_of, off_sorted, total_bytes;
+};
+
+BinGeometry bin_geometry(int B, int H, int W, int h, int hd, int r, int dtype, int rows)
+{
+    BinGeometry gmt{};
+    if (dtype == MATCHATTN_F32 || r != 1 || hd % 8 != 0 || hd > 40 || h > kBinItemsPerPass) return gmt;
+    const long long RB = 2LL * h * hd;
+    int TX = 16, TY = 8;
+    auto region = [&](int tx, int ty) { return (tx + 2 * r + 1LL) * (ty + 2 * r + 1LL) * RB; };
+    while (2 * region(TX, TY) > static_cast<long long>(kMaxBinnedSmem) && (TX > 1 || TY > 1)) {
+        if (TX >= TY * 2 || TY == 1) TX /= 2; else TY /= 2;
+    }
+    if (2 * region(TX, TY) > static_cast<long long>(kMaxBinnedSmem)) return gmt;
+    gmt.TX = TX; gmt.TY = TY;
+    gmt.RW = TX + 2 * r + 1; gmt.RH = TY + 2 * r + 1;
+    gmt.bins_x = (W + TX - 1) / TX; gmt.bins_y = (H + TY - 1) / TY;
+    const long long nbins = 1LL * B * gmt.bins_x * gmt.bins_y, nq = 1LL * B * rows * W;
+    if (nbins >= (1LL << 30) || nq >= (1LL << 31)) return gmt;
+    gmt.nbins = static_cast<int>(nbins);
+    gmt.region_bytes = static_cast<int>(region(TX, TY));
+    auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+    size_t off = 0;
+    gmt.off_counts = off;  off += 4 * static_cast<size_t>(nbins);      // counts and ctrl are cleared together
+    gmt.off_ctrl = off;    off = up(off + 4 * kCtrlWords);
+    gmt.off_starts = off;  off = up(off + 4 * static_cast<size_t>(nbins));
+    gmt.off_cursors = off; off = up(off + 4 * static_cast<size_t>(nbins));
+    gmt.off_bin_of = off;  off = up(off + 4 * static_cast<size_t>(nq));
+    gmt.off_sorted = off;  off = up(off + 8 * static_cast<size_t>(nq));
+    gmt.total_bytes = off;
+    gmt.valid = true;
+    return gmt;
+}
 constexpr int kMmaItemsPerBlock = 1024;   // 8 warps x 128 items
 
 inline bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -108,7 +149,7 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
 int forward_impl(const void *max_offset, const void *q, const void *k, const void *v, void *out, void *attn_out,
                  int B, int H, int W, int h, int hd, int rx, int ry, int dtype, int attn_type, float scale,
                  int q_row_begin, int q_row_end, void *cuda_stream, int tile_w, int force_generic, int cpl_request,
-                 int variant)
+                 int variant, void *workspace = nullptr, size_t workspace_bytes = 0, int strategy = kStrategyDirect)
 {
     if (!max_offset || !q || !k || !v || !out) return MATCHATTN_ERR_NULL;
     if (dtype != MATCHATTN_F32 && dtype != MATCHATTN_F16 && dtype != MATCHATTN_BF16) return MATCHATTN_ERR_DTYPE;
@@ -155,7 +196,48 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     p.N = static_cast<int>(N);
     p.r = r;
     p.scale = scale;
+    p.guard = nullptr;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+
+    // binned path: sort the queries by target tile, serve each tile from shared memory
+    if (strategy != kStrategyDirect) {
+        const BinGeometry gmt = bin_geometry(B, H, W, h, hd, r, dtype, p.rows);
+        const bool usable = gmt.valid && pl.fast && pl.lph == 1 && workspace != nullptr &&
+                            workspace_bytes >= gmt.total_bytes && aligned(workspace, 256) &&
+                            aligned(q, 16) && aligned(k, 16) && aligned(v, 16) && aligned(out, 16) &&
+                            aligned(attn_out, 32) && aligned(max_offset, 4);
+        if (strategy == kStrategyBinned && !usable) return MATCHATTN_ERR_VARIANT;
+        // The sorting passes and the one-block-per-tile staging do not yet beat the direct kernel on
+        // the shapes measured so far, so the automatic choice stays with the direct kernel and the
+        // binned path runs on request.
+        (void)kBinnedMinQueries;
+        if (usable && strategy == kStrategyBinned) {
+            char *ws = static_cast<char *>(workspace);
+            BinParams bp{};
+            bp.p = p;
+            bp.counts = reinterpret_cast<uint32_t *>(ws + gmt.off_counts);
+            bp.ctrl = reinterpret_cast<uint32_t *>(ws + gmt.off_ctrl);
+            bp.starts = reinterpret_cast<uint32_t *>(ws + gmt.off_starts);
+            bp.cursors = reinterpret_cast<uint32_t *>(ws + gmt.off_cursors);
+            bp.bin_of = reinterpret_cast<uint32_t *>(ws + gmt.off_bin_of);
+            bp.sorted = reinterpret_cast<uint2 *>(ws + gmt.off_sorted);
+            bp.bins_x = gmt.bins_x; bp.bins_y = gmt.bins_y; bp.nbins = gmt.nbins;
+            bp.TX = gmt.TX; bp.TY = gmt.TY; bp.RW = gmt.RW; bp.RH = gmt.RH; bp.region_bytes = gmt.region_bytes;
+            cudaError_t err = cudaMemsetAsync(bp.counts, 0, 4 * static_cast<size_t>(gmt.nbins) + 4 * kCtrlWords, stream);
+            if (err != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(err);
+            int dev = 0, sms = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            const int grid_blocks = 2 * (sms > 0 ? sms : 148);
+            const size_t smem_bytes = 2 * static_cast<size_t>(gmt.region_bytes);
+            err = dtype == MATCHATTN_F16 ? launch_binned<__half>(bp, pl.cpl, grid_blocks, smem_bytes, stream)
+                                         : launch_binned<__nv_bfloat16>(bp, pl.cpl, grid_blocks, smem_bytes, stream);
+            if (err != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(err);
+            // queries whose heads look at different places: the direct kernel below runs instead
+            p.guard = bp.ctrl + kCtrlNotShared;
+            pl.mma = false;
+        }
+    }
     switch (dtype) {
     case MATCHATTN_F32: return run<float>(p, pl, r, tile_w, stream);
     case MATCHATTN_F16: return run<__half>(p, pl, r, tile_w, stream);
@@ -184,6 +266,24 @@ int matchattn_fused_forward_ex(const void *max_offset, const void *q, const void
     return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
                                    scale, q_row_begin, q_row_end, cuda_stream, tile_w, force_generic,
                                    chunks_per_lane, variant);
+}
+
+size_t matchattn_workspace_bytes(int B, int H, int W, int h, int hd, int r, int dtype, int q_row_begin, int q_row_end)
+{
+    if (B <= 0 || H <= 0 || W <= 0 || h <= 0 || hd <= 0 || q_row_begin < 0 || q_row_end > H || q_row_begin >= q_row_end)
+        return 0;
+    const matchattn::BinGeometry gmt = matchattn::bin_geometry(B, H, W, h, hd, r, dtype, q_row_end - q_row_begin);
+    return gmt.valid ? gmt.total_bytes : 0;
+}
+
+int matchattn_fused_forward_ws(const void *max_offset, const void *q, const void *k, const void *v, void *out,
+                               void *attn_out, int B, int H, int W, int h, int hd, int rx, int ry, int dtype,
+                               int attn_type, float scale, int q_row_begin, int q_row_end, void *cuda_stream,
+                               void *workspace, size_t workspace_bytes, int strategy)
+{
+    return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
+                                   scale, q_row_begin, q_row_end, cuda_stream, 0, 0, 0, 0, workspace,
+                                   workspace_bytes, strategy);
 }
 
 const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned)

@@ -47,6 +47,7 @@ struct Params {
     int tile_h;
     int tiles_x;
     float scale;
+    const uint32_t *guard;   // when not null the kernel runs only if *guard != 0 (see matchattn_binned.cuh)
 };
 
 // ------------------------------------------------------------------ loads / stores
@@ -453,6 +454,8 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     constexpr int EPW = DT<T>::kElemsPerWord;
     constexpr int SLICE = CPL * 8;                          // channels per lane
 
+    if (p.guard != nullptr && *p.guard == 0u) return;
+
     // lane -> (query of the tile, head, slice of the head)
     const int tid = threadIdx.x;
     const int lq = tid / p.G;
@@ -582,6 +585,7 @@ __device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16 *p, float
 template <typename T>
 __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params p)
 {
+    if (p.guard != nullptr && *p.guard == 0u) return;
     const int64_t per_item = static_cast<int64_t>(p.Nq) * p.h;
     const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     if (t >= per_item) return;

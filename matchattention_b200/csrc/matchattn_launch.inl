@@ -3,6 +3,7 @@
 #include "matchattn_kernels.cuh"
 #ifdef MATCHATTN_T_IS_16BIT
 #include "matchattn_mma.cuh"
+#include "matchattn_binned.cuh"
 #endif
 
 namespace matchattn {
@@ -45,6 +46,40 @@ cudaError_t launch_mma<MATCHATTN_T>(const Params &p, int r, int cpl, dim3 grid, 
     MA_CASE(1) MA_CASE(2) MA_CASE(3) MA_CASE(4) MA_CASE(5)
 #undef MA_CASE
     return cudaErrorInvalidValue;
+}
+
+template <typename T, int CPL>
+static cudaError_t launch_binned_cpl(const BinParams &bp, int grid_blocks, size_t smem_bytes, cudaStream_t stream)
+{
+    static bool configured = false;      // per instantiation; a repeated set is harmless
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(binned_forward_kernel<T, CPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kMaxBinnedSmem));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    binned_forward_kernel<T, CPL><<<grid_blocks, kBinThreads, smem_bytes, stream>>>(bp);
+    return cudaGetLastError();
+}
+
+template <>
+cudaError_t launch_binned<MATCHATTN_T>(const BinParams &bp, int cpl, int grid_blocks, size_t smem_bytes,
+                                       cudaStream_t stream)
+{
+    const Params &p = bp.p;
+    const long long total = 1LL * p.B * p.Nq;
+    const unsigned qblocks = static_cast<unsigned>((total + 255) / 256);
+    bin_count_kernel<MATCHATTN_T, 1><<<qblocks, 256, 0, stream>>>(bp);
+    bin_scan_kernel<<<1, 1024, 0, stream>>>(bp);
+    bin_scatter_kernel<<<qblocks, 256, 0, stream>>>(bp);
+    switch (cpl) {
+    case 1: return launch_binned_cpl<MATCHATTN_T, 1>(bp, grid_blocks, smem_bytes, stream);
+    case 2: return launch_binned_cpl<MATCHATTN_T, 2>(bp, grid_blocks, smem_bytes, stream);
+    case 3: return launch_binned_cpl<MATCHATTN_T, 3>(bp, grid_blocks, smem_bytes, stream);
+    case 4: return launch_binned_cpl<MATCHATTN_T, 4>(bp, grid_blocks, smem_bytes, stream);
+    case 5: return launch_binned_cpl<MATCHATTN_T, 5>(bp, grid_blocks, smem_bytes, stream);
+    default: return cudaErrorInvalidValue;
+    }
 }
 #endif
 

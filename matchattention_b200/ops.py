@@ -66,13 +66,43 @@ def _check_tensors(max_offset, q, k, v, output, attn_out, H, W, rows, attn_num):
     return B, h, C // h
 
 
+STRATEGY_AUTO, STRATEGY_DIRECT, STRATEGY_BINNED = 0, 1, 2
+
+# scratch for the binned path, one buffer per (device, stream): calls on one stream are ordered, so
+# they can share it; calls on different streams may overlap on the device and must not
+_workspaces = {}
+
+
+def workspace_bytes(B: int, H: int, W: int, h: int, hd: int, r: int, dtype: torch.dtype, q_row_begin: int = 0,
+                    q_row_end: Optional[int] = None) -> int:
+    """Scratch bytes the binned path needs for these sizes (0: it does not apply)."""
+    return int(_lib.lib.matchattn_workspace_bytes(B, H, W, h, hd, r, _DTYPE_CODE[dtype], q_row_begin,
+                                                  H if q_row_end is None else q_row_end))
+
+
+def _workspace(device: torch.device, stream_id: int, nbytes: int) -> torch.Tensor:
+    key = (device.index, stream_id)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
 def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_type: str = "l1_norm",
            scale: float = 1.0, q_row_begin: int = 0, q_row_end: Optional[int] = None, *,
-           tile_w: int = 0, force_generic: bool = False, chunks_per_lane: int = 0, variant: int = 0) -> None:
-    """Validate, then enqueue the fused kernel on the current stream of q's device.
+           tile_w: int = 0, force_generic: bool = False, chunks_per_lane: int = 0, variant: int = 0,
+           strategy: int = STRATEGY_AUTO, workspace: Optional[torch.Tensor] = None) -> None:
+    """Validate, then enqueue the operator on the current stream of q's device.
 
     ``attn_out`` may be None (the attention weights are then not written).  With
     a row band, the query-side tensors hold rows [q_row_begin, q_row_end) only.
+    ``strategy``: 0 lets the library choose (currently the direct kernel), 1 forces
+    the direct kernel, 2 the binned path (queries sorted by target tile, K/V tiles
+    staged in shared memory; 16-bit types, r = 1, head width <= 40).  The binned path needs scratch
+    memory: ``workspace`` (a uint8 CUDA tensor) or, by default, a buffer this module
+    keeps per device and stream.  The tuning knobs (tile_w, force_generic,
+    chunks_per_lane, variant) belong to the direct kernels and imply strategy 1.
     """
     rx, ry = _window_radius(win_r)
     if q_row_end is None:
@@ -81,13 +111,28 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
         raise NotImplementedError(f"attn_type {attn_type!r}: only 'l1_norm' is implemented")
     attn_num = (2 * rx + 2) * (2 * ry + 2)
     B, h, hd = _check_tensors(max_offset, q, k, v, output, attn_out, H, W, q_row_end - q_row_begin, attn_num)
+    knobs = tile_w or force_generic or chunks_per_lane or variant
+    if knobs and strategy == STRATEGY_BINNED:
+        raise ValueError("the direct-kernel knobs cannot be combined with strategy=2")
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
-        status = _lib.lib.matchattn_fused_forward_ex(
-            max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
-            attn_out.data_ptr() if attn_out is not None else None,
-            B, H, W, h, hd, rx, ry, _DTYPE_CODE[q.dtype], _lib.L1_NORM, float(scale),
-            q_row_begin, q_row_end, stream, int(tile_w), int(bool(force_generic)), int(chunks_per_lane), int(variant))
+        args = (max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
+                attn_out.data_ptr() if attn_out is not None else None,
+                B, H, W, h, hd, rx, ry, _DTYPE_CODE[q.dtype], _lib.L1_NORM, float(scale),
+                q_row_begin, q_row_end, stream)
+        if knobs or strategy == STRATEGY_DIRECT:
+            status = _lib.lib.matchattn_fused_forward_ex(*args, int(tile_w), int(bool(force_generic)),
+                                                         int(chunks_per_lane), int(variant))
+        else:
+            need = workspace_bytes(B, H, W, h, hd, rx, q.dtype, q_row_begin, q_row_end) if rx == ry else 0
+            ws_ptr, ws_len = None, 0
+            if need:
+                if workspace is None:
+                    workspace = _workspace(q.device, stream, need)
+                if workspace.device != q.device or workspace.dtype != torch.uint8 or not workspace.is_contiguous():
+                    raise ValueError("workspace must be a contiguous uint8 tensor on q's device")
+                ws_ptr, ws_len = workspace.data_ptr(), workspace.numel()
+            status = _lib.lib.matchattn_fused_forward_ws(*args, ws_ptr, ws_len, int(strategy))
     _lib.check(status)
 
 
