@@ -54,6 +54,7 @@ extern "C" {
 #define MATCHATTN_ERR_ALIGN          7  /* a pointer is not aligned to its element size       */
 #define MATCHATTN_ERR_TOO_LARGE      8  /* sizes overflow the 32-bit index ranges in use      */
 #define MATCHATTN_ERR_VARIANT        9  /* the kernel variant asked for does not cover the arguments */
+#define MATCHATTN_ERR_SCRATCH_LIMIT 10  /* the problem needs more than the built-in scratch area     */
 #define MATCHATTN_ERR_CUDA         100  /* 100 + cudaError_t of a failed launch               */
 
 /* largest window radius accepted */
@@ -137,6 +138,39 @@ MATCHATTN_API int matchattn_fused_forward_ws(const void *max_offset, const void 
 /* Scratch bytes the binned path needs for these sizes; 0 when it does not apply. */
 MATCHATTN_API size_t matchattn_workspace_bytes(int B, int H, int W, int h, int hd, int r, int dtype,
                                                int q_row_begin, int q_row_end);
+
+/*
+ * The binned path for callers that cannot allocate device memory (a server whose
+ * memory plan is frozen after start-up, a frame loop with a fixed device budget, a
+ * host application that owns every allocation and hands a plugin only tensors and a
+ * stream).  Same arguments and results as matchattn_fused_forward_ws with strategy 2,
+ * but the scratch is a fixed area inside the library image, so the caller passes
+ * none and the library allocates none: no cudaMalloc, cudaFree or other allocating
+ * call is made.
+ *
+ *   - The area is MATCHATTN_STATIC_SCRATCH_BYTES large.  Every GPU on which the
+ *     library's module is loaded holds that much device memory until the process
+ *     exits.  A problem that needs more (see matchattn_workspace_bytes) is refused
+ *     with MATCHATTN_ERR_SCRATCH_LIMIT; one the binned path does not cover
+ *     (float32, r != 1, head width > 40) with MATCHATTN_ERR_VARIANT.  With the
+ *     present size, 8 heads x 16 channels in float16 fit up to about 690 000
+ *     queries per call (the 4 x 384 x 384 headline shape needs 7.1 MB).
+ *   - The first call on a device looks up the device address of the area (once per
+ *     device, with that device current).  Make that first call outside any stream
+ *     capture.
+ *   - All calls on a device share the one area and it keeps whatever the last call
+ *     left in it.  Each call clears the parts that must start at zero itself, on
+ *     its own stream.  Two calls that can overlap on the device (different streams,
+ *     different host threads) race on it: serialise them, or give the others
+ *     their own scratch through matchattn_fused_forward_ws.
+ * No counterpart in the reference.
+ */
+#define MATCHATTN_STATIC_SCRATCH_BYTES (8u << 20)
+MATCHATTN_API int matchattn_fused_forward_static(const void *max_offset, const void *q, const void *k, const void *v,
+                                                 void *out, void *attn_out,
+                                                 int B, int H, int W, int h, int hd, int rx, int ry,
+                                                 int dtype, int attn_type, float scale,
+                                                 int q_row_begin, int q_row_end, void *cuda_stream);
 
 /* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */

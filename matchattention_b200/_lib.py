@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libmatchattn_b200.so")
 
 # every symbol include/matchattn.h declares
 EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_fused_forward_ws",
-           "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
+           "matchattn_fused_forward_static", "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
 
 F32, F16, BF16 = 0, 1, 2
 L1_NORM = 0
@@ -34,6 +34,8 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_fused_forward_ex.argtypes = base + [_i, _i, _i, _i]
     lib.matchattn_fused_forward_ws.restype = _i
     lib.matchattn_fused_forward_ws.argtypes = base + [_vp, ctypes.c_size_t, _i]
+    lib.matchattn_fused_forward_static.restype = _i
+    lib.matchattn_fused_forward_static.argtypes = base
     lib.matchattn_workspace_bytes.restype = ctypes.c_size_t
     lib.matchattn_workspace_bytes.argtypes = [_i] * 9
     lib.matchattn_describe_dispatch.restype = ctypes.c_char_p

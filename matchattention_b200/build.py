@@ -2,7 +2,7 @@
 
     python -m matchattention_b200.build [--force]
 
-The four translation units (C ABI + one per element type) are compiled in
+The translation units (C ABI, one per element type, the built-in scratch area) are compiled in
 parallel and linked into matchattention_b200/lib/libmatchattn_b200.so.  The
 library carries its own static CUDA runtime and has no Python or torch
 dependency.
@@ -22,8 +22,9 @@ OBJ_DIR = os.path.join(PKG, "build")
 LIB_PATH = os.path.join(LIB_DIR, "libmatchattn_b200.so")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 
-SOURCES = ["matchattn_api.cu", "matchattn_f32.cu", "matchattn_f16.cu", "matchattn_bf16.cu"]
-HEADERS = ["matchattn_kernels.cuh", "matchattn_launch.inl"]
+SOURCES = ["matchattn_api.cu", "matchattn_f32.cu", "matchattn_f16.cu", "matchattn_bf16.cu",
+           "matchattn_static_scratch.cu"]
+HEADERS = ["matchattn_kernels.cuh", "matchattn_launch.inl", "matchattn_mma.cuh", "matchattn_binned.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-Xptxas", "-v"]
 

@@ -316,6 +316,9 @@ const char *matchattn_strerror(int status)
     case MATCHATTN_ERR_ALIGN: return "a pointer is not aligned to its element size";
     case MATCHATTN_ERR_TOO_LARGE: return "sizes exceed the supported index range";
     case MATCHATTN_ERR_VARIANT: return "the requested kernel variant does not cover these arguments";
+    case MATCHATTN_ERR_SCRATCH_LIMIT:
+        return "the problem needs more scratch than the built-in area holds (MATCHATTN_STATIC_SCRATCH_BYTES); "
+               "use matchattn_fused_forward_ws with your own scratch or split the call";
     default: break;
     }
     if (status >= MATCHATTN_ERR_CUDA) return cudaGetErrorString(static_cast<cudaError_t>(status - MATCHATTN_ERR_CUDA));
