@@ -346,12 +346,29 @@ def main():
         h2d = sum(t.numel() * t.element_size() for t in host)
         d2h = host_out.numel() * host_out.element_size() + host_attn.numel() * host_attn.element_size()
 
+        # Batch items are independent, so the step is pipelined item by item over a few streams:
+        # the host->device copy of item i+1, the kernel of item i and the device->host copy of
+        # item i-1 overlap (the two copy directions use separate DMA engines).
+        lanes = [torch.cuda.Stream(device=dev) for _ in range(min(3, B))]
+        fork, joins = torch.cuda.Event(), [torch.cuda.Event() for _ in lanes]
+
         def e2e_step():
-            for d, s in zip(d_in, host):
-                d.copy_(s, non_blocking=True)
-            ma.launch(d_in[0], d_in[1], d_in[2], d_in[3], out, attn, H, W, (r, r), "l1_norm", wl["scale"], **knobs)
-            host_out.copy_(out, non_blocking=True)
-            host_attn.copy_(attn, non_blocking=True)
+            main = torch.cuda.current_stream()
+            fork.record(main)
+            for i in range(B):
+                st = lanes[i % len(lanes)]
+                if i < len(lanes):
+                    st.wait_event(fork)
+                with torch.cuda.stream(st):
+                    for d, s in zip(d_in, host):
+                        d[i:i + 1].copy_(s[i:i + 1], non_blocking=True)
+                    ma.launch(d_in[0][i:i + 1], d_in[1][i:i + 1], d_in[2][i:i + 1], d_in[3][i:i + 1], out[i:i + 1],
+                              attn[i:i + 1], H, W, (r, r), "l1_norm", wl["scale"], **knobs)
+                    host_out[i:i + 1].copy_(out[i:i + 1], non_blocking=True)
+                    host_attn[i:i + 1].copy_(attn[i:i + 1], non_blocking=True)
+            for st, ev in zip(lanes, joins):
+                ev.record(st)
+                main.wait_event(ev)
 
         e2e_steps = max(3, min(args.steps, 20))
         for _ in range(3):
@@ -369,7 +386,8 @@ def main():
             ms_e2e = float(t.item())
         e2e = {"value": queries_per_step / (ms_e2e / e2e_steps * 1e-3), "unit": "queries/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-               "ms_per_step": ms_e2e / e2e_steps}
+               "ms_per_step": ms_e2e / e2e_steps, "kernel_launches_per_step": B,
+               "pipeline": f"{B} batch items over {len(lanes)} streams, pinned host buffers"}
     if sampler:
         sampler.stop()
 
@@ -388,7 +406,7 @@ def main():
                          "algorithmic_bytes_per_query": bpq, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "kernel": ma.describe_dispatch(h, hd, r, dtype)},
             "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps,      # the device-resident timed region: one kernel per step
         }
         if e2e is not None:
             line["e2e"] = e2e

@@ -110,6 +110,29 @@ MATCHATTN_API int matchattn_fused_forward_ex(const void *max_offset, const void 
                                int tile_w, int force_generic, int chunks_per_lane, int variant);
 
 /*
+ * The operator with the caller's glue folded in.  In the reference, MatchAttention.forward
+ * clamps the centres before the op (models/attention_blocks.py:45-59,79) and, in the cross
+ * branch, multiplies the result by a gate and concatenates the attention weights to it before
+ * the output projection (models/attention_blocks.py:95-98); these are five small kernels and
+ * two extra passes over the outputs per call.  Here:
+ *   clamp_offsets    non-zero: every centre is first clamped to [r, W-1-r-1e-3] x [r, H-1-r-1e-3]
+ *                    in the tensor type (the upper bound rounded to that type), NaN kept;
+ *   gate             [B, Nq, h*hd] or NULL: out is rounded to the tensor type and then
+ *                    multiplied by it element-wise;
+ *   out_row_stride   elements from one query's out to the next (0 = h*hd);
+ *   attn_row_stride  elements from one query's attn_out to the next (0 = h*(2r+2)^2).
+ * With out = buf, attn_out = buf + h*hd and both strides = h*hd + h*(2r+2)^2 the kernel writes
+ * the concatenated [B, Nq, h*hd + h*(2r+2)^2] tensor the projection consumes.  Direct kernel only.
+ */
+MATCHATTN_API int matchattn_fused_forward_glue(const void *max_offset, const void *q, const void *k, const void *v,
+                                               const void *gate, void *out, void *attn_out,
+                                               int B, int H, int W, int h, int hd, int rx, int ry,
+                                               int dtype, int attn_type, float scale,
+                                               int q_row_begin, int q_row_end,
+                                               int clamp_offsets, long long out_row_stride,
+                                               long long attn_row_stride, void *cuda_stream);
+
+/*
  * The same operator with scratch memory from the caller, which opens the binned
  * path: the queries are counting-sorted by the tile of the token map their window
  * falls into and each tile of K/V is staged in shared memory once for all the
@@ -124,7 +147,10 @@ MATCHATTN_API int matchattn_fused_forward_ex(const void *max_offset, const void 
  *                    but two calls that overlap on the device must not share it;
  *   strategy         0 = let the library choose (currently always the direct kernel);
  *                    1 = direct kernel (workspace may be NULL);
- *                    2 = binned path, or MATCHATTN_ERR_VARIANT when it does not apply.
+ *                    2 = binned path, or MATCHATTN_ERR_VARIANT when it does not apply;
+ *                    3 = the sorting passes only, then the direct kernel walking the queries
+ *                        in sorted order (the tiles are then shared through L1 instead of
+ *                        shared memory; heads may look at different places).
  * Still allocates nothing and does not synchronise.  No counterpart in the reference
  * (its driver allocates its own temporaries, models/src/match_former_fused_forward.cu:492-508).
  */

@@ -5,6 +5,8 @@ Public surface:
 * ``MF_FusedForwardOps`` / ``fused_forward`` / ``fused_forward_ops`` -- the
   reference's operator interface for this path;
 * ``match_attention`` -- functional form with the row-band and skip-attn options;
+* ``cross_attention_core`` / ``self_attention_core`` -- the operator with the caller's
+  clamp, gate and concatenation folded in;
 * ``install_dropin()`` -- makes ``import match_attention`` resolve to this
   implementation so that the unmodified reference model runs on it with
   ``--mat_impl cuda``.
@@ -17,7 +19,7 @@ that the build module itself can be run from a tree without the library.)
 import importlib
 
 _OPS = ("MF_FusedForwardOps", "describe_dispatch", "fused_forward", "fused_forward_ops", "launch",
-        "match_attention", "workspace_bytes")
+        "match_attention", "workspace_bytes", "cross_attention_core", "self_attention_core", "launch_glue")
 __all__ = list(_OPS) + ["install_dropin", "abi_version"]
 
 

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libmatchattn_b200.so")
 
 # every symbol include/matchattn.h declares
 EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_fused_forward_ws",
-           "matchattn_fused_forward_static", "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
+           "matchattn_fused_forward_static", "matchattn_fused_forward_glue", "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
 
 F32, F16, BF16 = 0, 1, 2
 L1_NORM = 0
@@ -36,6 +36,9 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_fused_forward_ws.argtypes = base + [_vp, ctypes.c_size_t, _i]
     lib.matchattn_fused_forward_static.restype = _i
     lib.matchattn_fused_forward_static.argtypes = base
+    lib.matchattn_fused_forward_glue.restype = _i
+    lib.matchattn_fused_forward_glue.argtypes = [_vp] * 7 + [_i] * 9 + [_f, _i, _i, _i, ctypes.c_longlong,
+                                                 ctypes.c_longlong, _vp]
     lib.matchattn_workspace_bytes.restype = ctypes.c_size_t
     lib.matchattn_workspace_bytes.argtypes = [_i] * 9
     lib.matchattn_describe_dispatch.restype = ctypes.c_char_p

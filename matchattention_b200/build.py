@@ -46,7 +46,8 @@ def _stale() -> bool:
 
 def _compile(src: str) -> tuple[str, str]:
     obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-c", os.path.join(CSRC, src), "-o", obj]
+    extra = os.environ.get("MATCHATTN_NVCC_EXTRA", "").split()      # e.g. -DMATCHATTN_FAST_EXP=1 for experiments
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", INCLUDE, "-c", os.path.join(CSRC, src), "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed on {src}:\n{res.stdout}\n{res.stderr}")

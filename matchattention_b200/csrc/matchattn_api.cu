@@ -20,7 +20,7 @@ struct Plan {
 };
 
 constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2;
-constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2;
+constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2, kStrategySorted = 3;
 constexpr long long kBinnedMinQueries = 32768;   // below this the three sorting passes cost more than they save
 
 // Geometry of the binned path; valid == false when the arguments are outside what it covers.
@@ -33,7 +33,7 @@ struct BinGeometry {
 BinGeometry bin_geometry(int B, int H, int W, int h, int hd, int r, int dtype, int rows)
 {
     BinGeometry gmt{};
-    if (dtype == MATCHATTN_F32 || r != 1 || hd % 8 != 0 || hd > 40 || h > kBinItemsPerPass) return gmt;
+    if (dtype == MATCHATTN_F32 || r != 1 || hd % 8 != 0 || hd > 40 || h > 128) return gmt;
     const long long RB = 2LL * h * hd;
     int TX = 16, TY = 8;
     auto region = [&](int tx, int ty) { return (tx + 2 * r + 1LL) * (ty + 2 * r + 1LL) * RB; };
@@ -132,9 +132,15 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
         p.tile_h = qpb / tw;
         p.tiles_x = (p.W + p.tile_w - 1) / p.tile_w;
         const int tiles_y = (p.rows + p.tile_h - 1) / p.tile_h;
-        const long long blocks = 1LL * p.tiles_x * tiles_y;
+        long long blocks = 1LL * p.tiles_x * tiles_y;
+        unsigned grid_y = p.B;
+        if (p.sorted != nullptr) {       // one flat list of queries over all batch items
+            const long long per_block = 1LL * p.tile_w * p.tile_h;
+            blocks = (1LL * p.B * p.Nq + per_block - 1) / per_block;
+            grid_y = 1;
+        }
         if (blocks > 2147483647LL) return MATCHATTN_ERR_TOO_LARGE;
-        const dim3 grid(static_cast<unsigned>(blocks), p.B);
+        const dim3 grid(static_cast<unsigned>(blocks), grid_y);
         err = pl.mma ? launch_mma_if_16bit<T>(p, r, pl.cpl, grid, stream)
                      : launch_fast<T>(p, r, pl.cpl, pl.lph > 1, grid, stream);
     } else {
@@ -146,10 +152,18 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
     return err == cudaSuccess ? MATCHATTN_OK : MATCHATTN_ERR_CUDA + static_cast<int>(err);
 }
 
+// caller-side glue folded into the call (matchattn_fused_forward_glue); all off by default
+struct Glue {
+    const void *gate = nullptr;
+    int clamp = 0;
+    long long out_stride = 0, attn_stride = 0;      // 0 = natural
+};
+
 int forward_impl(const void *max_offset, const void *q, const void *k, const void *v, void *out, void *attn_out,
                  int B, int H, int W, int h, int hd, int rx, int ry, int dtype, int attn_type, float scale,
                  int q_row_begin, int q_row_end, void *cuda_stream, int tile_w, int force_generic, int cpl_request,
-                 int variant, void *workspace = nullptr, size_t workspace_bytes = 0, int strategy = kStrategyDirect)
+                 int variant, void *workspace = nullptr, size_t workspace_bytes = 0, int strategy = kStrategyDirect,
+                 const Glue &glue = Glue())
 {
     if (!max_offset || !q || !k || !v || !out) return MATCHATTN_ERR_NULL;
     if (dtype != MATCHATTN_F32 && dtype != MATCHATTN_F16 && dtype != MATCHATTN_BF16) return MATCHATTN_ERR_DTYPE;
@@ -164,6 +178,13 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     // index ranges the kernels rely on: per-item offsets in 32 bits, batch on grid.y
     if (C > 65536 || N * C >= 2147483647LL || Nq * h * M >= 2147483647LL || B > 65535) return MATCHATTN_ERR_TOO_LARGE;
     const uintptr_t esize = dtype == MATCHATTN_F32 ? 4 : 2;
+    const long long out_stride = glue.out_stride > 0 ? glue.out_stride : C;
+    const long long attn_stride = glue.attn_stride > 0 ? glue.attn_stride : 1LL * h * M;
+    if (out_stride < C || attn_stride < 1LL * h * M || out_stride >= (1LL << 30) || attn_stride >= (1LL << 30))
+        return MATCHATTN_ERR_SHAPE;
+    const bool has_glue = glue.gate != nullptr || glue.clamp != 0 || out_stride != C || attn_stride != 1LL * h * M;
+    if (has_glue && (strategy == kStrategyBinned || variant == kVariantMma)) return MATCHATTN_ERR_VARIANT;
+    if (!aligned(glue.gate, esize)) return MATCHATTN_ERR_ALIGN;
     if (!aligned(max_offset, 2 * esize) || !aligned(q, esize) || !aligned(k, esize) || !aligned(v, esize) ||
         !aligned(out, esize) || !aligned(attn_out, esize))
         return MATCHATTN_ERR_ALIGN;
@@ -175,7 +196,8 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
         const uintptr_t need = (slice_bytes % 32 == 0) ? 32 : 16;
         const uintptr_t need_attn = (M * esize) % 32 == 0 ? 32 : ((M * esize) % 16 == 0 ? 16 : 8);
         if (!aligned(q, need) || !aligned(k, need) || !aligned(v, need) || !aligned(out, need) ||
-            !aligned(attn_out, need_attn))
+            !aligned(attn_out, need_attn) || !aligned(glue.gate, need) || (out_stride * esize) % need != 0 ||
+            (attn_stride * esize) % need_attn != 0)
             pl.fast = false;
     }
     if (pl.fast) {
@@ -197,6 +219,20 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     p.r = r;
     p.scale = scale;
     p.guard = nullptr;
+    p.sorted = nullptr;
+    p.gate = glue.gate;
+    p.out_stride = static_cast<int>(out_stride);
+    p.attn_stride = static_cast<int>(attn_stride);
+    p.clamp = glue.clamp;
+    if (glue.clamp) {
+        // the caller's bounds (models/attention_blocks.py:49-52), rounded to the tensor type as there
+        const float hx = static_cast<float>(W - 1 - r - 1e-3), hy = static_cast<float>(H - 1 - r - 1e-3);
+        p.clamp_lo = static_cast<float>(r);
+        p.clamp_hi_x = dtype == MATCHATTN_F16   ? __half2float(__float2half_rn(hx))
+                       : dtype == MATCHATTN_BF16 ? __bfloat162float(__float2bfloat16_rn(hx)) : hx;
+        p.clamp_hi_y = dtype == MATCHATTN_F16   ? __half2float(__float2half_rn(hy))
+                       : dtype == MATCHATTN_BF16 ? __bfloat162float(__float2bfloat16_rn(hy)) : hy;
+    }
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
 
     // binned path: sort the queries by target tile, serve each tile from shared memory
@@ -206,12 +242,12 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
                             workspace_bytes >= gmt.total_bytes && aligned(workspace, 256) &&
                             aligned(q, 16) && aligned(k, 16) && aligned(v, 16) && aligned(out, 16) &&
                             aligned(attn_out, 32) && aligned(max_offset, 4);
-        if (strategy == kStrategyBinned && !usable) return MATCHATTN_ERR_VARIANT;
+        if ((strategy == kStrategyBinned || strategy == kStrategySorted) && !usable) return MATCHATTN_ERR_VARIANT;
         // The sorting passes and the one-block-per-tile staging do not yet beat the direct kernel on
         // the shapes measured so far, so the automatic choice stays with the direct kernel and the
         // binned path runs on request.
         (void)kBinnedMinQueries;
-        if (usable && strategy == kStrategyBinned) {
+        if (usable && (strategy == kStrategyBinned || strategy == kStrategySorted)) {
             char *ws = static_cast<char *>(workspace);
             BinParams bp{};
             bp.p = p;
@@ -230,12 +266,18 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
             const int grid_blocks = 2 * (sms > 0 ? sms : 148);
             const size_t smem_bytes = 2 * static_cast<size_t>(gmt.region_bytes);
-            err = dtype == MATCHATTN_F16 ? launch_binned<__half>(bp, pl.cpl, grid_blocks, smem_bytes, stream)
-                                         : launch_binned<__nv_bfloat16>(bp, pl.cpl, grid_blocks, smem_bytes, stream);
+            const int main_cpl = strategy == kStrategySorted ? 0 : pl.cpl;     // 0: sorting passes only
+            err = dtype == MATCHATTN_F16 ? launch_binned<__half>(bp, main_cpl, grid_blocks, smem_bytes, stream)
+                                         : launch_binned<__nv_bfloat16>(bp, main_cpl, grid_blocks, smem_bytes, stream);
             if (err != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(err);
-            // queries whose heads look at different places: the direct kernel below runs instead
-            p.guard = bp.ctrl + kCtrlNotShared;
-            pl.mma = false;
+            if (strategy == kStrategySorted) {
+                // the direct kernel below walks the queries in sorted order; correct whatever the heads do
+                p.sorted = bp.sorted;
+            } else {
+                // queries whose heads look at different places: the direct kernel below runs instead
+                p.guard = bp.ctrl + kCtrlNotShared;
+                pl.mma = false;
+            }
         }
     }
     switch (dtype) {
@@ -266,6 +308,22 @@ int matchattn_fused_forward_ex(const void *max_offset, const void *q, const void
     return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
                                    scale, q_row_begin, q_row_end, cuda_stream, tile_w, force_generic,
                                    chunks_per_lane, variant);
+}
+
+int matchattn_fused_forward_glue(const void *max_offset, const void *q, const void *k, const void *v,
+                                 const void *gate, void *out, void *attn_out, int B, int H, int W, int h, int hd,
+                                 int rx, int ry, int dtype, int attn_type, float scale, int q_row_begin,
+                                 int q_row_end, int clamp_offsets, long long out_row_stride,
+                                 long long attn_row_stride, void *cuda_stream)
+{
+    matchattn::Glue glue;
+    glue.gate = gate;
+    glue.clamp = clamp_offsets;
+    glue.out_stride = out_row_stride;
+    glue.attn_stride = attn_row_stride;
+    return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
+                                   scale, q_row_begin, q_row_end, cuda_stream, 0, 0, 0, 0, nullptr, 0,
+                                   matchattn::kStrategyDirect, glue);
 }
 
 size_t matchattn_workspace_bytes(int B, int H, int W, int h, int hd, int r, int dtype, int q_row_begin, int q_row_end)

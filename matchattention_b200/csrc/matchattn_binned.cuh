@@ -35,8 +35,8 @@ namespace matchattn {
 enum { kCtrlBinCounter = 0, kCtrlNotShared = 1, kCtrlWords = 8 };
 
 constexpr size_t kMaxBinnedSmem = 112 * 1024;  // dynamic shared memory of one block (two blocks per SM)
-constexpr int kBinThreads = 128;              // threads of a block of pass 4 (two blocks per SM)
-constexpr int kBinItemsPerPass = 4 * 128;     // 4 warps x 128 items
+constexpr int kBinThreads = 256;              // threads of a block of pass 4 (two blocks per SM)
+constexpr int kBinItemsPerPass = (kBinThreads / 32) * 128;
 
 struct BinParams {
     Params p;
@@ -187,12 +187,16 @@ __device__ __forceinline__ void stg_item(char *ptr, const uint32_t (&w)[NW], uin
     for (int c = 0; c < NW / 4; ++c) st_128(ptr + ((16u * c) ^ swz), &w[4 * c]);
 }
 
-template <typename T, int CPL>
+// SAMEQ: the head count is a multiple of 8, so the two column halves of a row (columns t and t+4)
+// are two heads of the SAME query and share its window; then a lane handles 2 queries x 2 heads
+// and keeps one set of window coordinates per query instead of one per item.
+template <typename T, int CPL, bool SAMEQ>
 __global__ void __launch_bounds__(kBinThreads, 2) binned_forward_kernel(const BinParams bp)
 {
     constexpr int R = 1, SIDE = 2 * R + 2, M = SIDE * SIDE;
     constexpr int NW = CPL * 4;
     constexpr int SLICE = CPL * 8;
+    constexpr int NQ = SAMEQ ? 2 : 4;             // distinct windows per lane
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_bin;
 
@@ -243,71 +247,96 @@ __global__ void __launch_bounds__(kBinThreads, 2) binned_forward_kernel(const Bi
         }
         __syncthreads();
 
+        // each warp takes 128-item chunks of the bin on its own; the block meets again at the next bin
         const int items = cnt * p.h;
-        for (int pass0 = 0; pass0 < items; pass0 += kBinItemsPerPass) {
+        for (int pass0 = warp * 128; pass0 < items; pass0 += kBinItemsPerPass) {
+            // item i4 = 2*rowhalf + colhalf; window wq(i4) = its index into the per-query arrays
             bool valid[4];
             uint32_t qid[4];
             int head_of[4];
-            int col[4][SIDE], row[4][SIDE];        // byte offsets inside a region
-            uint32_t wgt[4][2];
+            int col[NQ][SIDE], row[NQ][SIDE];        // byte offsets inside a region, head 0
+            uint32_t wgt[NQ][2];
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4) {
-                const int item = pass0 + warp * 128 + (g + 8 * (i4 >> 1)) * 8 + t + 4 * (i4 & 1);
+                const int item = pass0 + (g + 8 * (i4 >> 1)) * 8 + t + 4 * (i4 & 1);
                 int sq = item / p.h;
-                const int head = item - sq * p.h;
+                head_of[i4] = item - sq * p.h;
                 valid[i4] = sq < cnt;
+                if (SAMEQ && (i4 & 1)) {               // same query as the item to its left
+                    qid[i4] = qid[i4 - 1];
+                    continue;
+                }
                 sq = min(sq, cnt - 1);
                 const uint2 rec = bp.sorted[start + sq];
                 qid[i4] = rec.x;
-                head_of[i4] = head;
+                const int wq = SAMEQ ? (i4 >> 1) : i4;
                 float x, y;
                 centre_from_bits<T>(rec.y, x, y);
                 const float xf = floorf(x), yf = floorf(y);
                 {
                     float wf[4];
                     bilinear_weights<T>(x, xf, y, yf, wf);
-                    wgt[i4][0] = DT<T>::pack(&wf[0]);
-                    wgt[i4][1] = DT<T>::pack(&wf[2]);
+                    wgt[wq][0] = DT<T>::pack(&wf[0]);
+                    wgt[wq][1] = DT<T>::pack(&wf[2]);
                 }
                 const int x0 = window_origin(xf, R, p.W) - R, y0 = window_origin(yf, R, p.H) - R;
 #pragma unroll
                 for (int i = 0; i < SIDE; ++i) {
-                    col[i4][i] = (min(max(x0 + i, 0), p.W - 1) - rx0) * RB + head * (SLICE * 2);
-                    row[i4][i] = (min(max(y0 + i, 0), p.H - 1) - ry0) * bp.RW * RB;
+                    col[wq][i] = (min(max(x0 + i, 0), p.W - 1) - rx0) * RB;
+                    row[wq][i] = (min(max(y0 + i, 0), p.H - 1) - ry0) * bp.RW * RB;
                 }
             }
+            int hoff[4];                              // byte offset of the item's head inside a token row
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4) hoff[i4] = head_of[i4] * (SLICE * 2);
+#define MA_WQ(i4_) (SAMEQ ? ((i4_) >> 1) : (i4_))
 
             uint32_t qw[4][NW];
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4)
-                ldg_item<NW>(qw[i4], static_cast<const char *>(p.q) + (static_cast<int64_t>(qid[i4]) * p.C + head_of[i4] * SLICE) * 2, swz);
+                ldg_item<NW>(qw[i4], static_cast<const char *>(p.q) + static_cast<int64_t>(qid[i4]) * RB + hoff[i4], swz);
 
+            // ---- scores
             uint32_t sc[M][2];
 #pragma unroll
             for (int j = 0; j < SIDE; ++j)
 #pragma unroll
                 for (int i = 0; i < SIDE; ++i) {
-                    uint32_t d[4][NW];
+                    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                    {
+                        uint32_t da[NW], db[NW];       // column half 0: items 0 (row g) and 2 (row g+8)
+                        lds_item<NW>(da, k_sm + row[MA_WQ(0)][j] + col[MA_WQ(0)][i] + hoff[0], swz);
+                        lds_item<NW>(db, k_sm + row[MA_WQ(2)][j] + col[MA_WQ(2)][i] + hoff[2], swz);
 #pragma unroll
-                    for (int i4 = 0; i4 < 4; ++i4) lds_item<NW>(d[i4], k_sm + row[i4][j] + col[i4][i], swz);
+                        for (int w = 0; w < NW; ++w) {
+                            da[w] = Mma<T>::absdiff2(qw[0][w], da[w]);
+                            db[w] = Mma<T>::absdiff2(qw[2][w], db[w]);
+                        }
 #pragma unroll
-                    for (int i4 = 0; i4 < 4; ++i4)
+                        for (int jj = 0; jj < NW / 2; ++jj)
+                            Mma<T>::run(c0, da[2 * jj], db[2 * jj], da[2 * jj + 1], db[2 * jj + 1], b_col0, b_col0);
+                    }
+                    {
+                        uint32_t da[NW], db[NW];       // column half 1: items 1 and 3
+                        lds_item<NW>(da, k_sm + row[MA_WQ(1)][j] + col[MA_WQ(1)][i] + hoff[1], swz);
+                        lds_item<NW>(db, k_sm + row[MA_WQ(3)][j] + col[MA_WQ(3)][i] + hoff[3], swz);
 #pragma unroll
-                        for (int w = 0; w < NW; ++w) d[i4][w] = Mma<T>::absdiff2(qw[i4][w], d[i4][w]);
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+                        for (int w = 0; w < NW; ++w) {
+                            da[w] = Mma<T>::absdiff2(qw[1][w], da[w]);
+                            db[w] = Mma<T>::absdiff2(qw[3][w], db[w]);
+                        }
 #pragma unroll
-                    for (int jj = 0; jj < NW / 2; ++jj)
-                        Mma<T>::run(c, d[0][2 * jj], d[2][2 * jj], d[0][2 * jj + 1], d[2][2 * jj + 1], b_col0, b_col0);
-#pragma unroll
-                    for (int jj = 0; jj < NW / 2; ++jj)
-                        Mma<T>::run(c, d[1][2 * jj], d[3][2 * jj], d[1][2 * jj + 1], d[3][2 * jj + 1], b_col1, b_col1);
-                    float fs[4];
-#pragma unroll
-                    for (int i4 = 0; i4 < 4; ++i4) fs[i4] = finish_score<T>(c[i4], p.scale);
+                        for (int jj = 0; jj < NW / 2; ++jj)
+                            Mma<T>::run(c1, da[2 * jj], db[2 * jj], da[2 * jj + 1], db[2 * jj + 1], b_col1, b_col1);
+                    }
+                    // the selectors leave c0's odd and c1's even entries at zero
+                    const float fs[4] = {finish_score<T>(c0[0], p.scale), finish_score<T>(c1[1], p.scale),
+                                         finish_score<T>(c0[2], p.scale), finish_score<T>(c1[3], p.scale)};
                     sc[j * SIDE + i][0] = DT<T>::pack(&fs[0]);
                     sc[j * SIDE + i][1] = DT<T>::pack(&fs[2]);
                 }
 
+            // ---- BilinearSoftmax per item
             uint32_t ap[4][M / 2];
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4) {
@@ -316,56 +345,48 @@ __global__ void __launch_bounds__(kBinThreads, 2) binned_forward_kernel(const Bi
 #pragma unroll
                     for (int m = 0; m < M; ++m) s[m] = DT<T>::unpack(sc[m][i4 >> 1], i4 & 1);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) wf[e] = DT<T>::unpack(wgt[i4][e >> 1], e & 1);
+                    for (int e = 0; e < 4; ++e) wf[e] = DT<T>::unpack(wgt[MA_WQ(i4)][e >> 1], e & 1);
                     bilinear_softmax<T, R>(s, wf, ap[i4]);
                 }
                 if (p.attn != nullptr && valid[i4])
                     store_words<M / 2>(static_cast<T *>(p.attn) + (static_cast<int64_t>(qid[i4]) * p.h + head_of[i4]) * M, ap[i4]);
             }
 
-            float o[2][NW][4];
+            // ---- values: one column half after the other, two taps per matrix instruction
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch)
+            for (int ch = 0; ch < 2; ++ch) {
+                float o[NW][4];
 #pragma unroll
                 for (int w = 0; w < NW; ++w)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) o[ch][w][e] = 0.f;
+                    for (int e = 0; e < 4; ++e) o[w][e] = 0.f;
+                const int ia = ch, ib = 2 + ch;       // the items of rows g and g+8
 #pragma unroll
-            for (int m = 0; m < M; m += 2) {
-                const int j0 = m / SIDE, i0 = m % SIDE, j1 = (m + 1) / SIDE, i1 = (m + 1) % SIDE;
+                for (int m = 0; m < M; m += 2) {
+                    const int j0 = m / SIDE, i0 = m % SIDE, j1 = (m + 1) / SIDE, i1 = (m + 1) % SIDE;
+                    uint32_t va0[NW], va1[NW], vb0[NW], vb1[NW];
+                    lds_item<NW>(va0, v_sm + row[MA_WQ(ia)][j0] + col[MA_WQ(ia)][i0] + hoff[ia], swz);
+                    lds_item<NW>(va1, v_sm + row[MA_WQ(ia)][j1] + col[MA_WQ(ia)][i1] + hoff[ia], swz);
+                    lds_item<NW>(vb0, v_sm + row[MA_WQ(ib)][j0] + col[MA_WQ(ib)][i0] + hoff[ib], swz);
+                    lds_item<NW>(vb1, v_sm + row[MA_WQ(ib)][j1] + col[MA_WQ(ib)][i1] + hoff[ib], swz);
+                    const uint32_t a_lo = dup_lo(ap[ia][m / 2]), a_hi = dup_hi(ap[ia][m / 2]);
+                    const uint32_t b_lo = dup_lo(ap[ib][m / 2]), b_hi = dup_hi(ap[ib][m / 2]);
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t v0[2][NW], v1[2][NW];
+                    for (int w = 0; w < NW; ++w)
+                        Mma<T>::run(o[w], Mma<T>::mul2(a_lo, va0[w]), Mma<T>::mul2(b_lo, vb0[w]),
+                                    Mma<T>::mul2(a_hi, va1[w]), Mma<T>::mul2(b_hi, vb1[w]), b_id, b_id);
+                }
 #pragma unroll
-                    for (int rh = 0; rh < 2; ++rh) {
-                        const int i4 = 2 * rh + ch;
-                        lds_item<NW>(v0[rh], v_sm + row[i4][j0] + col[i4][i0], swz);
-                        lds_item<NW>(v1[rh], v_sm + row[i4][j1] + col[i4][i1], swz);
-                    }
+                for (int rh = 0; rh < 2; ++rh) {
+                    const int i4 = 2 * rh + ch;
+                    if (!valid[i4]) continue;
+                    uint32_t ow[NW];
 #pragma unroll
-                    for (int rh = 0; rh < 2; ++rh) {
-                        const int i4 = 2 * rh + ch;
-                        const uint32_t a_lo = dup_lo(ap[i4][m / 2]), a_hi = dup_hi(ap[i4][m / 2]);
-#pragma unroll
-                        for (int w = 0; w < NW; ++w) {
-                            v0[rh][w] = Mma<T>::mul2(a_lo, v0[rh][w]);
-                            v1[rh][w] = Mma<T>::mul2(a_hi, v1[rh][w]);
-                        }
-                    }
-#pragma unroll
-                    for (int w = 0; w < NW; ++w) Mma<T>::run(o[ch][w], v0[0][w], v0[1][w], v1[0][w], v1[1][w], b_id, b_id);
+                    for (int w = 0; w < NW; ++w) ow[w] = DT<T>::pack(&o[w][2 * rh]);
+                    stg_item<NW>(static_cast<char *>(p.out) + static_cast<int64_t>(qid[i4]) * RB + hoff[i4], ow, swz);
                 }
             }
-
-#pragma unroll
-            for (int i4 = 0; i4 < 4; ++i4) {
-                if (!valid[i4]) continue;
-                const int rh = i4 >> 1, ch = i4 & 1;
-                uint32_t ow[NW];
-#pragma unroll
-                for (int w = 0; w < NW; ++w) ow[w] = DT<T>::pack(&o[ch][w][2 * rh]);
-                stg_item<NW>(static_cast<char *>(p.out) + (static_cast<int64_t>(qid[i4]) * p.C + head_of[i4] * SLICE) * 2, ow, swz);
-            }
+#undef MA_WQ
         }
     }
 }

@@ -48,7 +48,17 @@ struct Params {
     int tiles_x;
     float scale;
     const uint32_t *guard;   // when not null the kernel runs only if *guard != 0 (see matchattn_binned.cuh)
+    const uint2 *sorted;     // when not null: queries are taken in this order (x = b*Nq + n), see matchattn_binned.cuh
+    // caller-side glue folded into the kernel (all off by default)
+    const void *gate;        // [B, Nq, C] or null: out is multiplied by it element-wise (after rounding to T)
+    int out_stride;          // elements between consecutive queries of out (C unless out is part of a wider row)
+    int attn_stride;         // elements between consecutive queries of attn_out (h*M by default)
+    int clamp;               // non-zero: clamp the centre to [lo, hi_x] x [lo, hi_y] first, as the caller would
+    float clamp_lo, clamp_hi_x, clamp_hi_y;   // bounds, already rounded to T
 };
+
+// torch.clamp semantics: NaN stays NaN
+__device__ __forceinline__ float clamp_keep_nan(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
 
 // ------------------------------------------------------------------ loads / stores
 
@@ -145,6 +155,8 @@ struct DT<float> {
     // o += a * v over the elements of one word (o points at this word's accumulators)
     static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o) { o[0] = fmaf(a, __uint_as_float(vw), o[0]); }
     static __device__ __forceinline__ uint32_t pack(const float *o) { return __float_as_uint(o[0]); }
+    // word of packed outputs times word of the gate, rounded to T
+    static __device__ __forceinline__ uint32_t gate_mul(uint32_t o, uint32_t gw) { return __float_as_uint(__fmul_rn(__uint_as_float(o), __uint_as_float(gw))); }
     // attention weights live in 32-bit words holding kElemsPerWord of them ("lo" element first)
     static __device__ __forceinline__ uint32_t aw_from(float lo, float) { return __float_as_uint(lo); }
     static __device__ __forceinline__ uint32_t aw_bcast(float w) { return __float_as_uint(w); }
@@ -192,6 +204,11 @@ struct DT<__half> {
     {
         const __half2 t = *reinterpret_cast<const __half2 *>(&w);
         return hi ? __high2float(t) : __low2float(t);
+    }
+    static __device__ __forceinline__ uint32_t gate_mul(uint32_t o, uint32_t gw)
+    {
+        const __half2 t = __hmul2_rn(*reinterpret_cast<const __half2 *>(&o), *reinterpret_cast<const __half2 *>(&gw));
+        return *reinterpret_cast<const uint32_t *>(&t);
     }
     static __device__ __forceinline__ uint32_t aw_from(float lo, float hi)
     {
@@ -255,6 +272,12 @@ struct DT<__nv_bfloat16> {
     {
         return __uint_as_float(hi ? (w & 0xffff0000u) : (w << 16));
     }
+    static __device__ __forceinline__ uint32_t gate_mul(uint32_t o, uint32_t gw)
+    {
+        const __nv_bfloat162 t = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162 *>(&o),
+                                            *reinterpret_cast<const __nv_bfloat162 *>(&gw));
+        return *reinterpret_cast<const uint32_t *>(&t);
+    }
     static __device__ __forceinline__ uint32_t aw_from(float lo, float hi)
     {
         const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
@@ -296,6 +319,9 @@ __device__ __forceinline__ float softmax_exp(float x)
     return expf(x);
 #endif
 }
+// Correctly rounded 1/x: the quotient e/den then matches the reference's division to the last
+// float32 bit or one off.  (The one-ulp approximate reciprocal was measured to flip enough 16-bit
+// roundings of dominant weights to push single outputs past the tolerance.)
 __device__ __forceinline__ float softmax_rcp(float x) { return __frcp_rn(x); }
 
 // Window origin: floor of the centre, limited to the range in which the
@@ -446,7 +472,10 @@ constexpr int min_blocks()
     return (DT<T>::kHalfPipe && CPL <= 2) ? 3 : 2;
 }
 
-template <typename T, int R, int CPL, bool MULTI>
+// EXTRAS selects the build of the kernel that also honours the rarely used Params fields (sorted
+// query order, guard, clamp, gate, strided outputs); the plain build ignores them and keeps the
+// hot path free of their branches and registers.
+template <typename T, int R, int CPL, bool MULTI, bool EXTRAS>
 __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forward_kernel(const Params p)
 {
     constexpr int SIDE = 2 * R + 2, M = SIDE * SIDE;
@@ -454,7 +483,9 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     constexpr int EPW = DT<T>::kElemsPerWord;
     constexpr int SLICE = CPL * 8;                          // channels per lane
 
-    if (p.guard != nullptr && *p.guard == 0u) return;
+    if constexpr (EXTRAS) {
+        if (p.guard != nullptr && *p.guard == 0u) return;
+    }
 
     // lane -> (query of the tile, head, slice of the head)
     const int tid = threadIdx.x;
@@ -468,24 +499,45 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
         head = g;
         sl = 0;
     }
-    const int tile_y = blockIdx.x / p.tiles_x;
-    const int tile_x = blockIdx.x - tile_y * p.tiles_x;
-    int qx = tile_x * p.tile_w + (lq & (p.tile_w - 1));
-    int qy = tile_y * p.tile_h + (lq >> p.tile_w_shift);
-    const bool valid = (lq >> p.tile_w_shift) < p.tile_h && qx < p.W && qy < p.rows;
-    if constexpr (!MULTI) {
-        if (!valid) return;
+    bool valid;
+    int b;
+    int64_t bq;
+    if (EXTRAS && p.sorted != nullptr) {
+        // queries in the order of the sorted list: neighbours in the list look at the same tile of
+        // the map, so their taps hit in L1
+        const int qpb = p.tile_w * p.tile_h;
+        const int64_t total = static_cast<int64_t>(p.B) * p.Nq;
+        const int64_t qs = static_cast<int64_t>(blockIdx.x) * qpb + lq;
+        valid = lq < qpb && qs < total;
+        if constexpr (!MULTI) {
+            if (!valid) return;
+        }
+        bq = p.sorted[min(qs, total - 1)].x;
+        b = static_cast<int>(bq / p.Nq);
     } else {
-        // lanes without a query stay for the shuffles and redo a neighbour's work
-        qx = min(qx, p.W - 1);
-        qy = min(qy, p.rows - 1);
+        const int tile_y = blockIdx.x / p.tiles_x;
+        const int tile_x = blockIdx.x - tile_y * p.tiles_x;
+        int qx = tile_x * p.tile_w + (lq & (p.tile_w - 1));
+        int qy = tile_y * p.tile_h + (lq >> p.tile_w_shift);
+        valid = (lq >> p.tile_w_shift) < p.tile_h && qx < p.W && qy < p.rows;
+        if constexpr (!MULTI) {
+            if (!valid) return;
+        } else {
+            // lanes without a query stay for the shuffles and redo a neighbour's work
+            qx = min(qx, p.W - 1);
+            qy = min(qy, p.rows - 1);
+        }
+        b = blockIdx.y;
+        bq = static_cast<int64_t>(b) * p.Nq + qy * p.W + qx;
     }
-    const int b = blockIdx.y;
-    const int64_t bq = static_cast<int64_t>(b) * p.Nq + qy * p.W + qx;
 
     // sampling centre -> origin, weights, clamped tap rows / columns (in elements)
     float x, y;
     DT<T>::load_xy(static_cast<const T *>(p.mo) + (bq * p.h + head) * 2, x, y);
+    if (EXTRAS && p.clamp) {
+        x = clamp_keep_nan(x, p.clamp_lo, p.clamp_hi_x);
+        y = clamp_keep_nan(y, p.clamp_lo, p.clamp_hi_y);
+    }
     const float xf = floorf(x), yf = floorf(y);
     float wgt[4];
     bilinear_weights<T>(x, xf, y, yf, wgt);
@@ -530,7 +582,8 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     uint32_t aw[NWA];
     bilinear_softmax<T, R>(s, wgt, aw);
 
-    if (p.attn != nullptr && sl == 0 && valid) store_words<NWA>(static_cast<T *>(p.attn) + (bq * p.h + head) * M, aw);
+    if (p.attn != nullptr && sl == 0 && valid)
+        store_words<NWA>(static_cast<T *>(p.attn) + (EXTRAS ? bq * p.attn_stride + head * M : (bq * p.h + head) * M), aw);
 
     // weighted sum of the value taps
     float o[NW * EPW];
@@ -551,7 +604,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
         uint32_t ow[NW];
 #pragma unroll
         for (int w = 0; w < NW; ++w) ow[w] = DT<T>::pack(&o[w * EPW]);
-        store_words<NW>(static_cast<T *>(p.out) + bq * p.C + lane_off, ow);
+        if (EXTRAS && p.gate != nullptr) {
+            uint32_t gw[NW];
+            load_words<NW>(gw, static_cast<const T *>(p.gate) + bq * p.C + lane_off);
+#pragma unroll
+            for (int w = 0; w < NW; ++w) ow[w] = DT<T>::gate_mul(ow[w], gw[w]);
+        }
+        store_words<NW>(static_cast<T *>(p.out) + bq * (EXTRAS ? p.out_stride : p.C) + lane_off, ow);
     }
 }
 
@@ -595,7 +654,11 @@ __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params 
     const int r = p.r, side = 2 * r + 2, sub = 2 * r + 1, M = side * side;
 
     const T *mo = static_cast<const T *>(p.mo) + (bq * p.h + head) * 2;
-    const float x = load_one<T>(mo), y = load_one<T>(mo + 1);
+    float x = load_one<T>(mo), y = load_one<T>(mo + 1);
+    if (p.clamp) {
+        x = clamp_keep_nan(x, p.clamp_lo, p.clamp_hi_x);
+        y = clamp_keep_nan(y, p.clamp_lo, p.clamp_hi_y);
+    }
     const float xf = floorf(x), yf = floorf(y);
     float wgt[4];
     bilinear_weights<T>(x, xf, y, yf, wgt);
@@ -635,10 +698,11 @@ __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params 
             }
     }
     if (p.attn != nullptr) {
-        T *ap = static_cast<T *>(p.attn) + (bq * p.h + head) * M;
+        T *ap = static_cast<T *>(p.attn) + bq * p.attn_stride + head * M;
         for (int m = 0; m < M; ++m) store_one<T>(ap + m, a[m]);
     }
-    T *op = static_cast<T *>(p.out) + bq * p.C + head * p.hd;
+    T *op = static_cast<T *>(p.out) + bq * p.out_stride + head * p.hd;
+    const T *gp = p.gate != nullptr ? static_cast<const T *>(p.gate) + bq * p.C + head * p.hd : nullptr;
     for (int c = 0; c < p.hd; ++c) {
         float acc = 0.f;
         for (int j = 0; j < side; ++j) {
@@ -650,6 +714,7 @@ __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params 
                 else acc += DT<T>::rnd(a[j * side + i] * vv);
             }
         }
+        if (gp != nullptr) acc = DT<T>::rnd(acc) * load_one<T>(gp + c);
         store_one<T>(op + c, acc);
     }
 }

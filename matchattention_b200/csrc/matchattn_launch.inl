@@ -11,9 +11,12 @@ namespace matchattn {
 template <typename T, int R>
 static cudaError_t launch_fast_r(const Params &p, int cpl, bool multi, dim3 grid, cudaStream_t stream)
 {
+    const bool extras = p.guard != nullptr || p.sorted != nullptr || p.gate != nullptr || p.clamp != 0 ||
+                        p.out_stride != p.C || p.attn_stride != p.h * (2 * R + 2) * (2 * R + 2);
 #define MA_CASE(CPL_, MULTI_)                                                              \
     if (cpl == CPL_ && multi == MULTI_) {                                                  \
-        fused_forward_kernel<T, R, CPL_, MULTI_><<<grid, kThreads, 0, stream>>>(p);        \
+        if (extras) fused_forward_kernel<T, R, CPL_, MULTI_, true><<<grid, kThreads, 0, stream>>>(p);   \
+        else fused_forward_kernel<T, R, CPL_, MULTI_, false><<<grid, kThreads, 0, stream>>>(p);         \
         return cudaGetLastError();                                                         \
     }
     MA_CASE(1, false) MA_CASE(1, true)
@@ -48,18 +51,25 @@ cudaError_t launch_mma<MATCHATTN_T>(const Params &p, int r, int cpl, dim3 grid, 
     return cudaErrorInvalidValue;
 }
 
-template <typename T, int CPL>
-static cudaError_t launch_binned_cpl(const BinParams &bp, int grid_blocks, size_t smem_bytes, cudaStream_t stream)
+template <typename T, int CPL, bool SAMEQ>
+static cudaError_t launch_binned_one(const BinParams &bp, int grid_blocks, size_t smem_bytes, cudaStream_t stream)
 {
     static bool configured = false;      // per instantiation; a repeated set is harmless
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(binned_forward_kernel<T, CPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kMaxBinnedSmem));
+        cudaError_t e = cudaFuncSetAttribute(binned_forward_kernel<T, CPL, SAMEQ>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxBinnedSmem));
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    binned_forward_kernel<T, CPL><<<grid_blocks, kBinThreads, smem_bytes, stream>>>(bp);
+    binned_forward_kernel<T, CPL, SAMEQ><<<grid_blocks, kBinThreads, smem_bytes, stream>>>(bp);
     return cudaGetLastError();
+}
+
+template <typename T, int CPL>
+static cudaError_t launch_binned_cpl(const BinParams &bp, int grid_blocks, size_t smem_bytes, cudaStream_t stream)
+{
+    return bp.p.h % 8 == 0 ? launch_binned_one<T, CPL, true>(bp, grid_blocks, smem_bytes, stream)
+                           : launch_binned_one<T, CPL, false>(bp, grid_blocks, smem_bytes, stream);
 }
 
 template <>
@@ -73,6 +83,7 @@ cudaError_t launch_binned<MATCHATTN_T>(const BinParams &bp, int cpl, int grid_bl
     bin_scan_kernel<<<1, 1024, 0, stream>>>(bp);
     bin_scatter_kernel<<<qblocks, 256, 0, stream>>>(bp);
     switch (cpl) {
+    case 0: return cudaGetLastError();       // sorting passes only
     case 1: return launch_binned_cpl<MATCHATTN_T, 1>(bp, grid_blocks, smem_bytes, stream);
     case 2: return launch_binned_cpl<MATCHATTN_T, 2>(bp, grid_blocks, smem_bytes, stream);
     case 3: return launch_binned_cpl<MATCHATTN_T, 3>(bp, grid_blocks, smem_bytes, stream);

@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_forward_mma_kernel(const Pa
             bilinear_softmax<T, R>(s, wf, ap[i4]);
         }
         if (p.attn != nullptr && valid[i4])
-            store_words<M / 2>(static_cast<T *>(p.attn) + (bq[i4] * p.h + head_of[i4]) * M, ap[i4]);
+            store_words<M / 2>(static_cast<T *>(p.attn) + bq[i4] * p.attn_stride + head_of[i4] * M, ap[i4]);
     }
 
     // ---- values: two taps per matrix instruction, column halves one after the other
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_forward_mma_kernel(const Pa
         uint32_t ow[NW];
 #pragma unroll
         for (int w = 0; w < NW; ++w) ow[w] = DT<T>::pack(&o[ch][w][2 * rh]);
-        store_words<NW>(static_cast<T *>(p.out) + bq[i4] * p.C + lane_off[i4], ow);
+        store_words<NW>(static_cast<T *>(p.out) + bq[i4] * p.out_stride + lane_off[i4], ow);
     }
 }
 

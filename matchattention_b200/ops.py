@@ -197,3 +197,52 @@ def match_attention(max_offset, q, k, v, H: int, W: int, r: int, scale: float, *
 def describe_dispatch(h: int, hd: int, r: int, dtype: torch.dtype, aligned32: bool = True) -> Optional[str]:
     res = _lib.lib.matchattn_describe_dispatch(h, hd, r, _DTYPE_CODE[dtype], int(aligned32))
     return res.decode() if res is not None else None
+
+
+# ---- the caller's glue folded into the kernel ------------------------------------------------
+
+def launch_glue(max_offset, q, k, v, gate, out_base, attn_base, H: int, W: int, r: int, scale: float, *,
+                clamp: bool, out_stride: int = 0, attn_stride: int = 0) -> None:
+    """Enqueue the direct kernel with clamp / gate / strided outputs (see matchattn_fused_forward_glue)."""
+    B, Nq, C = q.shape
+    h = max_offset.size(2)
+    M = (2 * r + 2) ** 2
+    for name, t in (("max_offset", max_offset), ("q", q), ("k", k), ("v", v), ("gate", gate)):
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != q.dtype or t.device != q.device or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous CUDA tensor of q's dtype on q's device")
+    if tuple(max_offset.shape) != (B, Nq, h, 2) or tuple(k.shape) != (B, H * W, C) or tuple(v.shape) != (B, H * W, C) \
+            or Nq != H * W or (gate is not None and tuple(gate.shape) != (B, Nq, C)):
+        raise ValueError("shape mismatch")
+    with torch.cuda.device(q.device):
+        status = _lib.lib.matchattn_fused_forward_glue(
+            max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            gate.data_ptr() if gate is not None else None, out_base, attn_base,
+            B, H, W, h, C // h, r, r, _DTYPE_CODE[q.dtype], _lib.L1_NORM, float(scale), 0, H,
+            int(bool(clamp)), int(out_stride), int(attn_stride), torch.cuda.current_stream().cuda_stream)
+    _lib.check(status)
+
+
+def cross_attention_core(max_offset, q, k, v, gate, H: int, W: int, r: int, scale: float, clamp: bool = True):
+    """What MatchAttention.forward does between its q/k/v/g projections and its output projection in
+    the cross branch (models/attention_blocks.py:79-98), in one kernel: clamp the centres, run the
+    operator, multiply by the gate and lay the result out as cat((g * x, attn), -1).
+
+    Returns a [B, N, C + h*(2r+2)^2] tensor ready for ``proj``."""
+    B, N, C = q.shape
+    h = max_offset.size(2)
+    M = (2 * r + 2) ** 2
+    width = C + h * M
+    buf = q.new_empty(B, N, width)
+    launch_glue(max_offset, q, k, v, gate, buf.data_ptr(), buf.data_ptr() + C * buf.element_size(), H, W, r, scale,
+                clamp=clamp, out_stride=width, attn_stride=width)
+    return buf
+
+
+def self_attention_core(max_offset, q, k, v, H: int, W: int, r: int, scale: float, clamp: bool = True):
+    """The self branch (models/attention_blocks.py:79-93,99): clamp + operator; the attention weights,
+    which that branch discards, are never written.  Returns out [B, N, C]."""
+    out = torch.empty_like(q)
+    launch_glue(max_offset, q, k, v, None, out.data_ptr(), None, H, W, r, scale, clamp=clamp)
+    return out
