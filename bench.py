@@ -36,6 +36,7 @@ WORKLOADS = {
     "op_384x384_b4_h8x16_r1_f16_flow_perhead": (4, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, True),
     "op_384x384_b4_h8x16_r1_f16_smooth": (4, 384, 384, 8, 16, 1, torch.float16, "self", 3.0, 0.0, True),
     "op_384x384_b1_h8x16_r1_f16_flow": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, False),
+    "op_384x384_b1_h8x16_r1_f16_smooth": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 3.0, 0.0, False),
     "op_104x208_b1_h8x16_r1_f32_cross": (1, 104, 208, 8, 16, 1, torch.float32, "cross", 16.0, 0.0, False),
 }
 DEFAULT_WORKLOAD = "op_384x384_b4_h8x16_r1_f16_flow"

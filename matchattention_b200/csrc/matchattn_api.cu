@@ -17,10 +17,11 @@ struct Plan {
     int cpl;   // chunks (8 channels) per lane
     int lph;   // lanes per head
     bool mma;  // 16-bit, one lane per head, r == 1: accumulate with matrix instructions
+    int mma_nch = 2;   // items per lane of that kernel: 2 * mma_nch
 };
 
-constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2;
-constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2, kStrategySorted = 3;
+constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2, kVariantMma2 = 3;   // 3: two items per lane
+constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2, kStrategySorted = 3, kStrategySortedMma = 4;
 constexpr long long kBinnedMinQueries = 32768;   // below this the three sorting passes cost more than they save
 
 // Geometry of the binned path; valid == false when the arguments are outside what it covers.
@@ -60,7 +61,11 @@ BinGeometry bin_geometry(int B, int H, int W, int h, int hd, int r, int dtype, i
     gmt.valid = true;
     return gmt;
 }
-constexpr int kMmaItemsPerBlock = 1024;   // 8 warps x 128 items
+inline bool is_pow2_float(float v)
+{
+    int e = 0;
+    return v > 0.f && frexpf(v, &e) == 0.5f;
+}
 
 inline bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 inline int ilog2(int v)
@@ -75,7 +80,7 @@ inline int ilog2(int v)
 // odd == 5), and the remaining power of two becomes lanes per head.
 Plan make_plan(int h, int hd, int r, int cpl_request)
 {
-    Plan pl{false, 0, 0, false};
+    Plan pl{false, 0, 0, false, 2};
     if (hd % 8 != 0 || (r != 1 && r != 2)) return pl;
     const int hd8 = hd / 8;
     int odd = hd8;
@@ -98,11 +103,39 @@ Plan make_plan(int h, int hd, int r, int cpl_request)
 
 inline bool aligned(const void *p, uintptr_t a) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// The matrix-instruction kernel: unsorted (walks the map in tiles) or in sorted order.  In sorted
+// order with h a multiple of 8 the shared-window build runs when the sorting pass found all heads
+// of every query looking at one place (guard word == 0) and the general build otherwise; both are
+// enqueued, one of them returns at once.
 template <typename T>
-cudaError_t launch_mma_if_16bit(const Params &p, int r, int cpl, dim3 grid, cudaStream_t stream)
+cudaError_t run_mma(Params p, int cpl, const uint32_t *not_shared_flag, int nch, cudaStream_t stream)
 {
-    if constexpr (sizeof(T) == 2) return launch_mma<T>(p, r, cpl, grid, stream);
-    else return cudaErrorInvalidValue;
+    if constexpr (sizeof(T) != 2) {
+        return cudaErrorInvalidValue;
+    } else {
+        const bool pow2 = is_pow2_float(p.scale);
+        long long items;
+        p.tiles_x = (p.W + kMmaTileW - 1) / kMmaTileW;
+        if (p.sorted != nullptr) {
+            items = 1LL * p.B * p.Nq * p.h;
+        } else {
+            const long long tiles_y = (p.rows + kMmaTileH - 1) / kMmaTileH;
+            items = 1LL * p.B * tiles_y * p.tiles_x * kMmaTileW * kMmaTileH * p.h;
+        }
+        const long long per_block = (kThreads / 32) * 64LL * nch;
+        if (items >= (1LL << 31) - per_block) return cudaErrorInvalidValue;
+        const unsigned blocks = static_cast<unsigned>((items + per_block - 1) / per_block);
+        if (nch == 2 && p.sorted != nullptr && not_shared_flag != nullptr && p.h % 8 == 0) {
+            p.guard = not_shared_flag;
+            p.guard_run_if = 0;
+            cudaError_t e = launch_mma<T>(p, cpl, true, pow2, 2, blocks, stream);
+            if (e != cudaSuccess) return e;
+            p.guard_run_if = 1;
+            return launch_mma<T>(p, cpl, false, pow2, 2, blocks, stream);
+        }
+        p.guard = nullptr;
+        return launch_mma<T>(p, cpl, false, pow2, nch, blocks, stream);
+    }
 }
 
 template <typename T>
@@ -113,8 +146,11 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
         p.lph = pl.lph;
         p.lph_shift = ilog2(pl.lph);
         p.G = p.h * pl.lph;
-        const int lanes_per_block = pl.mma ? kMmaItemsPerBlock : kThreads;
-        const int qpb = lanes_per_block / p.G;       // queries per block (>= 1)
+        if (pl.mma) {
+            err = run_mma<T>(p, pl.cpl, p.sorted != nullptr ? p.guard : nullptr, pl.mma_nch, stream);
+            return err == cudaSuccess ? MATCHATTN_OK : MATCHATTN_ERR_CUDA + static_cast<int>(err);
+        }
+        const int qpb = kThreads / p.G;              // queries per block (>= 1)
         const int qpw = p.G >= 32 ? 1 : 32 / p.G;    // queries a warp covers, kept in one row
         int tw;
         if (tile_w_request > 0) {
@@ -141,8 +177,7 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
         }
         if (blocks > 2147483647LL) return MATCHATTN_ERR_TOO_LARGE;
         const dim3 grid(static_cast<unsigned>(blocks), grid_y);
-        err = pl.mma ? launch_mma_if_16bit<T>(p, r, pl.cpl, grid, stream)
-                     : launch_fast<T>(p, r, pl.cpl, pl.lph > 1, grid, stream);
+        err = launch_fast<T>(p, r, pl.cpl, pl.lph > 1, grid, stream);
     } else {
         const long long per_item = 1LL * p.Nq * p.h;
         const long long blocks = (per_item + kThreads - 1) / kThreads;
@@ -183,13 +218,13 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     if (out_stride < C || attn_stride < 1LL * h * M || out_stride >= (1LL << 30) || attn_stride >= (1LL << 30))
         return MATCHATTN_ERR_SHAPE;
     const bool has_glue = glue.gate != nullptr || glue.clamp != 0 || out_stride != C || attn_stride != 1LL * h * M;
-    if (has_glue && (strategy == kStrategyBinned || variant == kVariantMma)) return MATCHATTN_ERR_VARIANT;
+    if (has_glue && (strategy == kStrategyBinned || variant == kVariantMma || variant == kVariantMma2)) return MATCHATTN_ERR_VARIANT;
     if (!aligned(glue.gate, esize)) return MATCHATTN_ERR_ALIGN;
     if (!aligned(max_offset, 2 * esize) || !aligned(q, esize) || !aligned(k, esize) || !aligned(v, esize) ||
         !aligned(out, esize) || !aligned(attn_out, esize))
         return MATCHATTN_ERR_ALIGN;
 
-    Plan pl = force_generic ? Plan{false, 0, 0, false} : make_plan(h, hd, r, cpl_request);
+    Plan pl = force_generic ? Plan{false, 0, 0, false, 2} : make_plan(h, hd, r, cpl_request);
     if (pl.fast) {
         // vector width of a lane's slice decides the alignment the specialised kernel needs
         const int slice_bytes = pl.cpl * 8 * static_cast<int>(esize);
@@ -201,12 +236,15 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
             pl.fast = false;
     }
     if (pl.fast) {
-        const bool mma_ok = esize == 2 && r == 1 && pl.lph == 1 && h <= kMmaItemsPerBlock;
-        // the direct-gather form of the matrix-instruction kernel runs at one block per SM and is
-        // latency-bound; it is selected only on request
-        pl.mma = mma_ok && variant == kVariantMma;
-        if (variant == kVariantMma && !mma_ok) return MATCHATTN_ERR_VARIANT;
-    } else if (variant == kVariantMma) {
+        // the matrix-instruction kernel addresses q/out, k/v and attn_out with 32-bit byte offsets
+        const bool mma_ok = esize == 2 && r == 1 && pl.lph == 1 && !has_glue && aligned(attn_out, 32) &&
+                            1LL * B * N * C * 2 < (1LL << 32) && 1LL * B * Nq * C * 2 < (1LL << 32) &&
+                            1LL * B * Nq * h * M * 2 < (1LL << 32);
+        const bool want_mma = variant == kVariantMma || variant == kVariantMma2 || strategy == kStrategySortedMma;
+        pl.mma = mma_ok && want_mma;
+        pl.mma_nch = variant == kVariantMma2 ? 1 : 2;
+        if (want_mma && !mma_ok) return MATCHATTN_ERR_VARIANT;
+    } else if (variant == kVariantMma || variant == kVariantMma2 || strategy == kStrategySortedMma) {
         return MATCHATTN_ERR_VARIANT;
     }
 
@@ -219,6 +257,7 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     p.r = r;
     p.scale = scale;
     p.guard = nullptr;
+    p.guard_run_if = 1;
     p.sorted = nullptr;
     p.gate = glue.gate;
     p.out_stride = static_cast<int>(out_stride);
@@ -242,12 +281,12 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
                             workspace_bytes >= gmt.total_bytes && aligned(workspace, 256) &&
                             aligned(q, 16) && aligned(k, 16) && aligned(v, 16) && aligned(out, 16) &&
                             aligned(attn_out, 32) && aligned(max_offset, 4);
-        if ((strategy == kStrategyBinned || strategy == kStrategySorted) && !usable) return MATCHATTN_ERR_VARIANT;
+        if (strategy >= kStrategyBinned && !usable) return MATCHATTN_ERR_VARIANT;
         // The sorting passes and the one-block-per-tile staging do not yet beat the direct kernel on
         // the shapes measured so far, so the automatic choice stays with the direct kernel and the
         // binned path runs on request.
         (void)kBinnedMinQueries;
-        if (usable && (strategy == kStrategyBinned || strategy == kStrategySorted)) {
+        if (usable && strategy >= kStrategyBinned) {
             char *ws = static_cast<char *>(workspace);
             BinParams bp{};
             bp.p = p;
@@ -266,13 +305,16 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
             const int grid_blocks = 2 * (sms > 0 ? sms : 148);
             const size_t smem_bytes = 2 * static_cast<size_t>(gmt.region_bytes);
-            const int main_cpl = strategy == kStrategySorted ? 0 : pl.cpl;     // 0: sorting passes only
+            const int main_cpl = strategy == kStrategyBinned ? pl.cpl : 0;     // 0: sorting passes only
             err = dtype == MATCHATTN_F16 ? launch_binned<__half>(bp, main_cpl, grid_blocks, smem_bytes, stream)
                                          : launch_binned<__nv_bfloat16>(bp, main_cpl, grid_blocks, smem_bytes, stream);
             if (err != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(err);
             if (strategy == kStrategySorted) {
                 // the direct kernel below walks the queries in sorted order; correct whatever the heads do
                 p.sorted = bp.sorted;
+            } else if (strategy == kStrategySortedMma) {
+                p.sorted = bp.sorted;
+                p.guard = bp.ctrl + kCtrlNotShared;      // picks the shared-window or the general build
             } else {
                 // queries whose heads look at different places: the direct kernel below runs instead
                 p.guard = bp.ctrl + kCtrlNotShared;

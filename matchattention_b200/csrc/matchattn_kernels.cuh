@@ -47,7 +47,8 @@ struct Params {
     int tile_h;
     int tiles_x;
     float scale;
-    const uint32_t *guard;   // when not null the kernel runs only if *guard != 0 (see matchattn_binned.cuh)
+    const uint32_t *guard;   // when not null the kernel runs only if (*guard != 0) == (guard_run_if != 0)
+    int guard_run_if;
     const uint2 *sorted;     // when not null: queries are taken in this order (x = b*Nq + n), see matchattn_binned.cuh
     // caller-side glue folded into the kernel (all off by default)
     const void *gate;        // [B, Nq, C] or null: out is multiplied by it element-wise (after rounding to T)
@@ -484,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     constexpr int SLICE = CPL * 8;                          // channels per lane
 
     if constexpr (EXTRAS) {
-        if (p.guard != nullptr && *p.guard == 0u) return;
+        if (p.guard != nullptr && ((*p.guard != 0u) != (p.guard_run_if != 0))) return;
     }
 
     // lane -> (query of the tile, head, slice of the head)
@@ -644,7 +645,7 @@ __device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16 *p, float
 template <typename T>
 __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params p)
 {
-    if (p.guard != nullptr && *p.guard == 0u) return;
+    if (p.guard != nullptr && ((*p.guard != 0u) != (p.guard_run_if != 0))) return;
     const int64_t per_item = static_cast<int64_t>(p.Nq) * p.h;
     const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     if (t >= per_item) return;

@@ -37,18 +37,31 @@ cudaError_t launch_fast<MATCHATTN_T>(const Params &p, int r, int cpl, bool multi
 }
 
 #ifdef MATCHATTN_T_IS_16BIT
-template <>
-cudaError_t launch_mma<MATCHATTN_T>(const Params &p, int r, int cpl, dim3 grid, cudaStream_t stream)
+template <typename T, int CPL>
+static cudaError_t launch_mma_cpl(const Params &p, bool sameq, bool pow2, int nch, unsigned blocks, cudaStream_t stream)
 {
-    if (r != 1) return cudaErrorInvalidValue;
-#define MA_CASE(CPL_)                                                                      \
-    if (cpl == CPL_) {                                                                     \
-        fused_forward_mma_kernel<MATCHATTN_T, 1, CPL_><<<grid, kThreads, 0, stream>>>(p);  \
-        return cudaGetLastError();                                                         \
+    if (nch == 1) {
+        if (pow2) fused_forward_mma_kernel<T, CPL, false, true, 1><<<blocks, kThreads, 0, stream>>>(p);
+        else fused_forward_mma_kernel<T, CPL, false, false, 1><<<blocks, kThreads, 0, stream>>>(p);
+    } else if (sameq && pow2) fused_forward_mma_kernel<T, CPL, true, true, 2><<<blocks, kThreads, 0, stream>>>(p);
+    else if (sameq) fused_forward_mma_kernel<T, CPL, true, false, 2><<<blocks, kThreads, 0, stream>>>(p);
+    else if (pow2) fused_forward_mma_kernel<T, CPL, false, true, 2><<<blocks, kThreads, 0, stream>>>(p);
+    else fused_forward_mma_kernel<T, CPL, false, false, 2><<<blocks, kThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <>
+cudaError_t launch_mma<MATCHATTN_T>(const Params &p, int cpl, bool sameq, bool pow2, int nch, unsigned blocks,
+                                    cudaStream_t stream)
+{
+    switch (cpl) {
+    case 1: return launch_mma_cpl<MATCHATTN_T, 1>(p, sameq, pow2, nch, blocks, stream);
+    case 2: return launch_mma_cpl<MATCHATTN_T, 2>(p, sameq, pow2, nch, blocks, stream);
+    case 3: return launch_mma_cpl<MATCHATTN_T, 3>(p, sameq, pow2, nch, blocks, stream);
+    case 4: return launch_mma_cpl<MATCHATTN_T, 4>(p, sameq, pow2, nch, blocks, stream);
+    case 5: return launch_mma_cpl<MATCHATTN_T, 5>(p, sameq, pow2, nch, blocks, stream);
+    default: return cudaErrorInvalidValue;
     }
-    MA_CASE(1) MA_CASE(2) MA_CASE(3) MA_CASE(4) MA_CASE(5)
-#undef MA_CASE
-    return cudaErrorInvalidValue;
 }
 
 template <typename T, int CPL, bool SAMEQ>

@@ -85,3 +85,38 @@ def test_binned_rejects_what_it_does_not_cover():
         ma.match_attention(mo, q, k, v, H, W, 1, 0.25, strategy=BINNED, workspace=small)
     assert ma.workspace_bytes(B, H, W, h, hd, 1, torch.float16) > 0
     assert ma.workspace_bytes(B, H, W, h, hd, 1, torch.float32) == 0
+
+
+SORTED, SORTED_MMA = 3, 4
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("knobs", [dict(strategy=SORTED), dict(strategy=SORTED_MMA), dict(variant=2), dict(variant=3)],
+                         ids=["sorted-scalar", "sorted-matrix", "matrix-4-items", "matrix-2-items"])
+@pytest.mark.parametrize("case", CASES + [(1, 40, 44, 8, 16, "flow", 6.0, True), (2, 30, 28, 4, 32, "self", 3.0, True)])
+def test_opt_in_kernels_match_oracle_and_direct(case, knobs, dtype):
+    """The other ways of running the same operator -- queries walked in sorted order, float32 sums on
+    the matrix instructions (four or two items per lane) -- against the oracle and the default kernel."""
+    import oracle
+    B, H, W, h, hd, kind, spread, per_head = case
+    inputs = make_inputs(50 + H + hd, B, H, W, h, hd, 1, dtype, kind=kind, spread=spread, border_frac=0.2,
+                         per_head=per_head)
+    ref_out, ref_attn = oracle.forward(*inputs, H, W, 1, hd ** -0.5)
+    out, attn = _run(inputs, H, W, hd, **knobs)
+    ties = hd > 16
+    assert_close(attn, ref_attn, dtype, "attn", ties=ties)
+    assert_close(out, ref_out, dtype, "out", ties=ties)
+    d_out, d_attn = _run(inputs, H, W, hd, strategy=1)
+    assert_close(attn, d_attn, dtype, "attn vs direct", ties=ties)
+    assert_close(out, d_out, dtype, "out vs direct", ties=ties)
+
+
+def test_matrix_kernel_row_band():
+    B, H, W, h, hd = 2, 45, 38, 4, 16
+    mo, q, k, v = make_inputs(64, B, H, W, h, hd, 1, torch.float16, kind="flow", spread=6.0)
+    full_out, full_attn = _run((mo, q, k, v), H, W, hd, variant=3)
+    r0, r1 = 7, 30
+    sl = slice(r0 * W, r1 * W)
+    out, attn = _run((mo[:, sl].contiguous(), q[:, sl].contiguous(), k, v), H, W, hd, variant=3,
+                     q_row_begin=r0, q_row_end=r1)
+    assert torch.equal(out, full_out[:, sl]) and torch.equal(attn, full_attn[:, sl])
