@@ -210,10 +210,60 @@ def run_band_mode(args, rank, local_rank, world):
         mo = torch.cat((mo[..., :1].clamp(r, W - 1 - r - 1e-3), mo[..., 1:].clamp(r, H - 1 - r - 1e-3)), -1)
         full = (mo.to(dtype).contiguous(), q, k, v)
 
+    from matchattention_b200.band import halo_rows
+    max_dy = 33.0 if args.band_kv == "halo" else None       # the synthetic flow is at most 32 tokens
+    r0, r1 = band_rows(H, world, rank)
+
+    # resident variant: every rank already holds its band of q / max_offset and keeps its band of the
+    # outputs (what a band-parallel caller would do); only K and V move each step
+    if args.band_resident and world > 1:
+        q_band = torch.empty(B, (r1 - r0) * W, C, dtype=dtype, device=dev)
+        mo_band = torch.empty(B, (r1 - r0) * W, h, 2, dtype=dtype, device=dev)
+        if rank == 0:
+            for pr in range(1, world):
+                p0, p1 = band_rows(H, world, pr)
+                dist.send(full[1][:, p0 * W:p1 * W].contiguous(), pr)
+                dist.send(full[0][:, p0 * W:p1 * W].contiguous(), pr)
+            q_band.copy_(full[1][:, r0 * W:r1 * W])
+            mo_band.copy_(full[0][:, r0 * W:r1 * W])
+            kv = [full[2], full[3]]
+        else:
+            dist.recv(q_band, 0)
+            dist.recv(mo_band, 0)
+        out_band = torch.empty_like(q_band)
+        attn_band = q_band.new_empty(B, (r1 - r0) * W, h, 16)
+
+    def replicate_kv():
+        if max_dy is None:
+            dist.broadcast(kv[0], src=0)
+            dist.broadcast(kv[1], src=0)
+        elif rank == 0:
+            ops, keep = [], []
+            for pr in range(1, world):
+                p0, p1 = band_rows(H, world, pr)
+                h0, h1 = halo_rows(H, p0, p1, r, max_dy)
+                for t in kv:
+                    keep.append(t[:, h0 * W:h1 * W].contiguous())
+                    ops.append(dist.P2POp(dist.isend, keep[-1], pr))
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        else:
+            h0, h1 = halo_rows(H, r0, r1, r, max_dy)
+            parts = [torch.empty(B, (h1 - h0) * W, C, dtype=dtype, device=dev) for _ in kv]
+            for req in dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, 0) for t in parts]):
+                req.wait()
+            kv[0][:, h0 * W:h1 * W] = parts[0]
+            kv[1][:, h0 * W:h1 * W] = parts[1]
+
     def step():
         if world == 1:
             return ma.match_attention(*full, H, W, r, hd ** -0.5)
-        return band_match_attention(*full, B, H, W, h, hd, r, hd ** -0.5, dtype, dev, kv_buffers=kv)
+        if args.band_resident:
+            replicate_kv()
+            return ma.match_attention(mo_band, q_band, kv[0], kv[1], H, W, r, hd ** -0.5, q_row_begin=r0,
+                                      q_row_end=r1, out=out_band, attn_out=attn_band)
+        return band_match_attention(*full, B, H, W, h, hd, r, hd ** -0.5, dtype, dev, kv_buffers=kv,
+                                    max_abs_dy=max_dy)
 
     def barrier():
         torch.cuda.synchronize()
@@ -240,13 +290,84 @@ def run_band_mode(args, rank, local_rank, world):
         line = {"metric": "matchattention_queries_per_s", "value": B * N / (ms_per_step * 1e-3), "unit": "queries/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": "op_1024x1024_b2_h4x32_r1_f16_rowband", "mode": "row bands, K/V broadcast",
+                "config": {"workload": "op_1024x1024_b2_h4x32_r1_f16_rowband",
+                           "mode": f"row bands, K/V {args.band_kv}" + (", q/out bands resident" if args.band_resident else ", q scattered and out gathered every step"),
                            "kv_broadcast_bytes_per_step": 2 * B * N * C * 2, "band_rows": band_rows(H, world, 0)},
                 "gpu_launches": args.steps}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_model_ops_mode(args):
+    """The 52 MatchAttention calls of one MatchStereo-T forward at 1536x1536 (both view directions, B=2,
+    4 heads): per stage the token map, channel count, window radius and number of layers of the
+    reference model; self-attention calls use small per-head offsets and skip attn_out, cross-attention
+    calls use one smooth disparity-like offset per query.  Timed eagerly and as one CUDA graph."""
+    import matchattention_b200 as ma
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = torch.float16
+    stages = [(48, 160, 2, 8), (96, 128, 2, 8), (192, 64, 1, 8), (384, 32, 1, 2)]      # side, C, r, layers
+    B, h = 2, 4
+    g = torch.Generator(device=dev).manual_seed(7)
+    calls, alg_bytes = [], 0
+    for side, C, r, layers in stages:
+        N, hd, M = side * side, C // h, (2 * r + 2) ** 2
+        q, k, v = (torch.randn(B, N, C, generator=g, device=dev).to(dtype) for _ in range(3))
+        ys, xs = torch.meshgrid(torch.arange(side, device=dev, dtype=torch.float32),
+                                torch.arange(side, device=dev, dtype=torch.float32), indexing="ij")
+        grid = torch.stack((xs, ys), -1).view(1, N, 1, 2)
+        coarse = torch.rand(B, 1, 7, 7, generator=g, device=dev) * (-side / 8.0)          # disparity up to 1/8 of the width
+        disp = torch.nn.functional.interpolate(coarse, size=(side, side), mode="bilinear", align_corners=True)
+        cross = grid + torch.cat((disp.view(B, N, 1, 1), torch.zeros(B, N, 1, 1, device=dev)), -1)
+        cross = cross.expand(B, N, h, 2)
+        selfo = grid + (torch.rand(B, N, h, 2, generator=g, device=dev) * 2 - 1)
+        def clamp(mo):
+            return torch.cat((mo[..., :1].clamp(r, side - 1 - r - 1e-3), mo[..., 1:].clamp(r, side - 1 - r - 1e-3)),
+                             -1).to(dtype).contiguous()
+        cross, selfo = clamp(cross), clamp(selfo)
+        out, attn = torch.empty_like(q), q.new_empty(B, N, h, M)
+        for _ in range(layers):
+            calls.append((selfo, q, k, v, out, None, side, r, hd))
+            calls.append((cross, q, k, v, out, attn, side, r, hd))
+            alg_bytes += 2 * B * N * (4 * C + 2 * h) + 2 * B * N * (4 * C + 2 * h + h * M)
+
+    def forward_ops():
+        for mo, q, k, v, out, attn, side, r, hd in calls:
+            ma.launch(mo, q, k, v, out, attn, side, side, (r, r), "l1_norm", hd ** -0.5)
+
+    def timed(fn, n):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    n = max(5, min(args.steps, 100))
+    eager_ms = timed(forward_ops, n)
+    graph = torch.cuda.CUDAGraph()
+    side_stream = torch.cuda.Stream()
+    with torch.cuda.stream(side_stream):
+        forward_ops()
+        with torch.cuda.graph(graph, stream=side_stream):
+            forward_ops()
+    torch.cuda.synchronize()
+    graph_ms = timed(graph.replay, n)
+    line = {"metric": "matchstereo_t_1536_op_sequence_ms_per_pair", "value": graph_ms, "unit": "ms", "n_gpus": 1,
+            "steps": n, "warmup": max(3, args.warmup), "ms_per_step": graph_ms, "higher_is_better": False,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "52 MatchAttention calls of MatchStereo-T at 1536x1536 (B=2, h=4)",
+                       "stages_side_C_r_layers": stages, "eager_ms": eager_ms, "cuda_graph_ms": graph_ms,
+                       "algorithmic_bytes": alg_bytes, "algorithmic_GBps_graph": alg_bytes / graph_ms / 1e6},
+            "gpu_launches": 52 * n}
+    print(json.dumps(line), flush=True)
 
 
 def config_dict(name, wl):
@@ -264,8 +385,13 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--mode", choices=["pairs", "band"], default="pairs",
-                    help="pairs: every GPU its own batch (default); band: one large pair split by query row bands")
+    ap.add_argument("--mode", choices=["pairs", "band", "model_ops"], default="pairs",
+                    help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
+                         "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
+    ap.add_argument("--band-kv", choices=["broadcast", "halo"], default="broadcast",
+                    help="band mode: replicate all of K/V (NCCL broadcast) or only the rows a band can reach")
+    ap.add_argument("--band-resident", action="store_true",
+                    help="band mode: q / max_offset / outputs stay distributed, only K/V move each step")
     ap.add_argument("--tile-w", type=int, default=0)
     ap.add_argument("--chunks-per-lane", type=int, default=0)
     ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 scalar kernel, 2 matrix-instruction kernel")
@@ -286,6 +412,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
     if args.mode == "band":
         run_band_mode(args, rank, local_rank, world)
+        return
+    if args.mode == "model_ops":
+        run_model_ops_mode(args)
         return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

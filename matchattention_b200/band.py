@@ -28,6 +28,14 @@ def band_rows(H: int, world: int, rank: int, r: int = 0) -> Tuple[int, int]:
     return r0, r0 + base + (1 if rank < extra else 0)
 
 
+def halo_rows(H: int, r0: int, r1: int, r: int, max_abs_dy: float) -> Tuple[int, int]:
+    """Key/value rows a band [r0, r1) can touch when no sampling centre lies more than
+    `max_abs_dy` rows away from its own query row: the window adds r rows above and r + 1 below
+    (floor + 2r + 2 taps), one more row covers the rounding of the bound."""
+    reach = int(max_abs_dy) + 1
+    return max(0, r0 - reach - r), min(H, r1 + reach + r + 2)
+
+
 def _default_op(mo, q, k, v, H, W, r, scale, r0, r1, need_attn):
     from .ops import match_attention
     return match_attention(mo, q, k, v, H, W, r, scale, need_attn=need_attn, q_row_begin=r0, q_row_end=r1)
@@ -42,13 +50,20 @@ def _p2p(ops: List) -> None:
 def band_match_attention(max_offset: Optional[torch.Tensor], q: Optional[torch.Tensor], k: Optional[torch.Tensor],
                          v: Optional[torch.Tensor], B: int, H: int, W: int, h: int, hd: int, r: int, scale: float,
                          dtype: torch.dtype, device: torch.device, *, src: int = 0, group=None,
-                         need_attn: bool = True, op: Optional[Callable] = None, kv_buffers=None):
+                         need_attn: bool = True, op: Optional[Callable] = None, kv_buffers=None,
+                         max_abs_dy: Optional[float] = None):
     """Run one MatchAttention call split by query row bands over the ranks of `group`.
 
     On rank `src` pass the full tensors (max_offset [B,H*W,h,2], q/k/v [B,H*W,C]); on the other
     ranks pass None.  Returns (out, attn) holding the full result on `src` and (None, None)
     elsewhere.  `op` replaces the band computation (tests run the CPU oracle through it);
     `kv_buffers` lets a caller reuse the (k, v) receive buffers between calls.
+
+    K and V are replicated with a broadcast.  If the caller can bound how far a sampling centre
+    lies from its query row (`max_abs_dy`, in rows; e.g. the flow magnitude limit of the model),
+    each rank instead receives only the rows its band can reach (halo_rows) by point-to-point
+    copies into its full-size buffer; rows outside stay untouched and are never read.  The bound
+    is the caller's promise: a centre beyond it reads stale rows.
     """
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     op = op or _default_op
@@ -65,13 +80,33 @@ def band_match_attention(max_offset: Optional[torch.Tensor], q: Optional[torch.T
         kk = torch.empty((B, N, C), dtype=dtype, device=device)
         vv = torch.empty((B, N, C), dtype=dtype, device=device)
     src_global = dist.get_global_rank(group, src) if group is not None else src
-    dist.broadcast(kk, src=src_global, group=group)
-    dist.broadcast(vv, src=src_global, group=group)
 
-    # band inputs: src slices and sends, the others receive
     def peer(p):
         return dist.get_global_rank(group, p) if group is not None else p
 
+    if max_abs_dy is None:
+        dist.broadcast(kk, src=src_global, group=group)
+        dist.broadcast(vv, src=src_global, group=group)
+    elif rank == src:
+        ops, keep = [], []
+        for p in range(world):
+            p0, p1 = band_rows(H, world, p)
+            if p == src or p1 == p0:
+                continue
+            h0, h1 = halo_rows(H, p0, p1, r, max_abs_dy)
+            for t in (kk, vv):
+                part = t[:, h0 * W:h1 * W].contiguous()
+                keep.append(part)
+                ops.append(dist.P2POp(dist.isend, part, peer(p), group))
+        _p2p(ops)
+    elif rows > 0:
+        h0, h1 = halo_rows(H, r0, r1, r, max_abs_dy)
+        parts = [torch.empty((B, (h1 - h0) * W, C), dtype=dtype, device=device) for _ in range(2)]
+        _p2p([dist.P2POp(dist.irecv, t, peer(src), group) for t in parts])
+        kk[:, h0 * W:h1 * W] = parts[0]
+        vv[:, h0 * W:h1 * W] = parts[1]
+
+    # band inputs: src slices and sends, the others receive
     if rank == src:
         ops, keep = [], []
         for p in range(world):

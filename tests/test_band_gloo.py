@@ -1,6 +1,7 @@
 """CPU tests of the row-band multi-GPU path: world_size 2 and 3 over gloo.  The band
 computation is injected (the CPU oracle), so what is tested is the partition, the
 broadcast of K/V, the movement of the band inputs and the reassembly of the outputs."""
+import math
 import os
 import sys
 
@@ -23,7 +24,19 @@ def test_band_rows_partition():
             assert max(sizes) - min(sizes) <= 1
 
 
-def _worker(rank, world, port, H, W, results):
+def test_halo_rows_cover_the_window():
+    from matchattention_b200.band import halo_rows
+    assert halo_rows(100, 0, 50, 1, 0.0) == (0, 54)
+    assert halo_rows(100, 50, 100, 2, 3.5) == (44, 100)
+    H, r = 64, 1
+    for r0, r1, dy in ((10, 20, 2.0), (0, 64, 5.0), (30, 31, 0.4)):
+        h0, h1 = halo_rows(H, r0, r1, r, dy)
+        lowest = max(0, math.floor(r0 - dy) - r)              # floor(y) - r for the most upward centre
+        highest = min(H - 1, math.floor(r1 - 1 + dy) + r + 1)    # floor(y) + r + 1 for the most downward one
+        assert h0 <= lowest and h1 > highest
+
+
+def _worker(rank, world, port, H, W, results, max_abs_dy=None):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -33,14 +46,20 @@ def _worker(rank, world, port, H, W, results):
         from _cases import make_inputs
         from matchattention_b200.band import band_match_attention
         B, h, hd, r = 2, 2, 8, 1
-        mo, q, k, v = make_inputs(31, B, H, W, h, hd, r, torch.float16, kind="flow", spread=4.0)
+        mo, q, k, v = make_inputs(31, B, H, W, h, hd, r, torch.float16, kind="flow", spread=4.0,
+                                  border_frac=0.1 if max_abs_dy is None else 0.0)
 
         def op(mo_b, q_b, kk, vv, H_, W_, r_, scale, r0, r1, need_attn):
             return oracle.forward(mo_b, q_b, kk, vv, H_, W_, r_, scale, q_row_begin=r0, q_row_end=r1, nthreads=1,
                                   want_attn=need_attn)
 
         args = (mo, q, k, v) if rank == 0 else (None, None, None, None)
-        out, attn = band_match_attention(*args, B, H, W, h, hd, r, 0.3, torch.float16, torch.device("cpu"), op=op)
+        kv = None
+        if max_abs_dy is not None and rank != 0:
+            # poison the receive buffers: rows outside the halo must never be read
+            kv = [torch.full((B, H * W, h * hd), float("nan"), dtype=torch.float16) for _ in range(2)]
+        out, attn = band_match_attention(*args, B, H, W, h, hd, r, 0.3, torch.float16, torch.device("cpu"), op=op,
+                                         kv_buffers=kv, max_abs_dy=max_abs_dy)
         if rank == 0:
             ref_out, ref_attn = oracle.forward(mo, q, k, v, H, W, r, 0.3, nthreads=1)
             results.put((bool(torch.equal(out, ref_out)), bool(torch.equal(attn, ref_attn))))
@@ -57,6 +76,22 @@ def test_band_split_reassembles_the_full_result(world, H):
     results = ctx.Queue()
     port = 29500 + (os.getpid() + world * 7 + H) % 2000
     procs = [ctx.Process(target=_worker, args=(rank, world, port, H, 8, results)) for rank in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert results.get(timeout=5) == (True, True)
+
+
+def test_band_split_with_halo_exchange():
+    """Offsets of at most 4 rows (the generator's spread): only the reachable K/V rows travel, the
+    rest of the receive buffers is NaN, and the result still equals the full one bit for bit."""
+    world, H = 3, 30
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = 29500 + (os.getpid() + 977) % 2000
+    procs = [ctx.Process(target=_worker, args=(rank, world, port, H, 8, results, 4.0)) for rank in range(world)]
     for p in procs:
         p.start()
     for p in procs:
