@@ -370,6 +370,37 @@ def run_model_ops_mode(args):
     print(json.dumps(line), flush=True)
 
 
+def run_upsample_mode(args):
+    """The convex upsampling of the field that follows the last MatchAttention block of MatchStereo at
+    1536x1536: field [2, 384, 384, 2] x 4, mask [2, 144, 384, 384], float16."""
+    import matchattention_b200 as ma
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, H, W, D, f, dtype = 2, 384, 384, 2, 4, torch.float16
+    g = torch.Generator(device=dev).manual_seed(3)
+    field = (torch.randn(B, H, W, D, generator=g, device=dev) * 4).to(dtype)
+    mask = (torch.randn(B, 9 * f * f, H, W, generator=g, device=dev) * 2).to(dtype)
+    n = max(20, args.steps)
+    for _ in range(max(3, args.warmup)):
+        out = ma.upsample_field(field, mask, f)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        out = ma.upsample_field(field, mask, f)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    nbytes = (field.numel() + mask.numel() + out.numel()) * 2
+    peak, kind = measured_peak()
+    print(json.dumps({"metric": "upsample_field_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": n,
+                      "higher_is_better": False, "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "upsample_field 2x384x384x2 by 4", "bytes": nbytes,
+                                 "note": "working set 106 MB fits the 126 MB L2: repeated calls are served from L2"},
+                      "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peak, "unit": "GB/s",
+                                   "frac": nbytes / ms / 1e6 / peak, "peak_kind": kind}}), flush=True)
+
+
 def config_dict(name, wl):
     return {"workload": name, "B_per_gpu": wl["B"], "token_map": [wl["H"], wl["W"]], "heads": wl["h"],
             "head_dim": wl["hd"], "win_r": wl["r"], "window_taps": (2 * wl["r"] + 2) ** 2,
@@ -385,7 +416,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--mode", choices=["pairs", "band", "model_ops"], default="pairs",
+    ap.add_argument("--mode", choices=["pairs", "band", "model_ops", "upsample"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
     ap.add_argument("--band-kv", choices=["broadcast", "halo"], default="broadcast",
@@ -415,6 +446,9 @@ def main():
         return
     if args.mode == "model_ops":
         run_model_ops_mode(args)
+        return
+    if args.mode == "upsample":
+        run_upsample_mode(args)
         return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

@@ -198,6 +198,19 @@ MATCHATTN_API int matchattn_fused_forward_static(const void *max_offset, const v
                                                  int dtype, int attn_type, float scale,
                                                  int q_row_begin, int q_row_end, void *cuda_stream);
 
+/*
+ * Convex upsampling of a field, the step either side of the operator in the model:
+ * MatchStereo.upsample_field (models/match_stereo.py:73-84) as one kernel instead of a
+ * softmax, an unfold, a broadcast product, a sum and a permute.
+ *   field [B, H, W, D]           D <= 8
+ *   mask  [B, 9*f*f, H, W]       channel (k*f + i)*f + j, k = 3x3 neighbour (row-major, zero padding)
+ *   out   [B, f*H, f*W, D]       written; f = factor in {1, 2, 4, 8}
+ *   out[b, h*f+i, w*f+j, d] = sum_k softmax_k(mask[b, (k,i,j), h, w]) * (f * field[b, h+ky-1, w+kx-1, d])
+ * Allocates nothing, launches on `cuda_stream`.
+ */
+MATCHATTN_API int matchattn_upsample_field(const void *field, const void *mask, void *out,
+                                           int B, int H, int W, int D, int factor, int dtype, void *cuda_stream);
+
 /* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */
 MATCHATTN_API const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned);

@@ -19,7 +19,8 @@ that the build module itself can be run from a tree without the library.)
 import importlib
 
 _OPS = ("MF_FusedForwardOps", "describe_dispatch", "fused_forward", "fused_forward_ops", "launch",
-        "match_attention", "workspace_bytes", "cross_attention_core", "self_attention_core", "launch_glue")
+        "match_attention", "workspace_bytes", "cross_attention_core", "self_attention_core", "launch_glue",
+        "upsample_field")
 __all__ = list(_OPS) + ["install_dropin", "abi_version"]
 
 

@@ -246,3 +246,25 @@ def self_attention_core(max_offset, q, k, v, H: int, W: int, r: int, scale: floa
     out = torch.empty_like(q)
     launch_glue(max_offset, q, k, v, None, out.data_ptr(), None, H, W, r, scale, clamp=clamp)
     return out
+
+
+def upsample_field(field: torch.Tensor, mask: torch.Tensor, factor: int) -> torch.Tensor:
+    """Convex upsampling of a field, same arguments and result as ``MatchStereo.upsample_field``
+    (models/match_stereo.py:73-84): field [B,H,W,D], mask [B,9*f*f,H,W] -> [B,f*H,f*W,D], one kernel."""
+    if not field.is_cuda:
+        raise RuntimeError("matchattn_b200 runs on CUDA tensors only (no CPU fallback); got device " + str(field.device))
+    if field.dtype not in _DTYPE_CODE or mask.dtype != field.dtype or mask.device != field.device:
+        raise TypeError("field and mask must share a supported dtype (float32, float16, bfloat16) and device")
+    if field.dim() != 4 or mask.dim() != 4:
+        raise ValueError("expected field [B,H,W,D] and mask [B,9*f*f,H,W]")
+    B, H, W, D = field.shape
+    if tuple(mask.shape) != (B, 9 * factor * factor, H, W):
+        raise ValueError(f"mask has shape {tuple(mask.shape)}, expected {(B, 9 * factor * factor, H, W)}")
+    field, mask = field.contiguous(), mask.contiguous()
+    out = field.new_empty(B, H * factor, W * factor, D)
+    with torch.cuda.device(field.device):
+        status = _lib.lib.matchattn_upsample_field(field.data_ptr(), mask.data_ptr(), out.data_ptr(), B, H, W, D,
+                                                   int(factor), _DTYPE_CODE[field.dtype],
+                                                   torch.cuda.current_stream().cuda_stream)
+    _lib.check(status)
+    return out

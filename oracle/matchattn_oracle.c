@@ -28,6 +28,9 @@
  * marks every place where such a rounding happens; for fp32 it is the
  * identity.
  *
+ * A second, smaller function restates the convex upsampling of a field that sits
+ * on either side of the operator in the model (models/match_stereo.py:73-84).
+ *
  * Layout (all arrays contiguous, row-major):
  *   max_offset [B, Nq, h, 2]   absolute (x, y) sampling centre in token units
  *   q          [B, Nq, h*hd]
@@ -318,5 +321,51 @@ int matchattn_oracle_forward(const void *max_offset, const void *q, const void *
     /* a thread that could not be started has its range done here */
     for (int t = started + 1; t < nthreads; ++t) run_job(&jobs[t]);
     for (int t = 1; t <= started; ++t) pthread_join(tids[t], NULL);
+    return 0;
+}
+
+/*
+ * Convex upsampling of a field, MatchStereo.upsample_field (models/match_stereo.py:73-84):
+ *   field [B, H, W, D], mask [B, 9*f*f, H, W] (channel = (k*f + i)*f + j, k = 3x3 neighbour, row-major,
+ *   zero padding), out [B, f*H, f*W, D]:
+ *   out[b, h*f+i, w*f+j, d] = sum_k softmax_k(mask[b, (k,i,j), h, w]) * (f * field[b, h+ky-1, w+kx-1, d]).
+ * Rounding in the 16-bit types as eager PyTorch: the softmax result, field*f and each product are
+ * rounded to the tensor type, the sum over the nine neighbours accumulates in float32.
+ */
+int matchattn_oracle_upsample_field(const void *field, const void *mask, void *out, int B, int H, int W, int D,
+                                    int factor, int dtype)
+{
+    if (!field || !mask || !out) return 1;
+    if (B <= 0 || H <= 0 || W <= 0 || D <= 0 || factor <= 0) return 2;
+    if (dtype != MA_F32 && dtype != MA_F16 && dtype != MA_BF16) return 4;
+    ensure_half_table();
+    const int dt = dtype, f = factor;
+    const int64_t plane = (int64_t)H * W;
+    for (int b = 0; b < B; ++b)
+        for (int h = 0; h < H; ++h)
+            for (int w = 0; w < W; ++w)
+                for (int i = 0; i < f; ++i)
+                    for (int j = 0; j < f; ++j) {
+                        float logit[9], mx = -INFINITY, den = 0.0f, p[9];
+                        for (int k = 0; k < 9; ++k) {
+                            const int64_t ch = ((int64_t)k * f + i) * f + j;
+                            logit[k] = load_elem(mask, ((int64_t)b * 9 * f * f + ch) * plane + (int64_t)h * W + w, dt);
+                            mx = logit[k] > mx ? logit[k] : mx;
+                        }
+                        for (int k = 0; k < 9; ++k) { p[k] = expf(logit[k] - mx); den += p[k]; }
+                        for (int k = 0; k < 9; ++k) p[k] = RND(p[k] / den);
+                        for (int d = 0; d < D; ++d) {
+                            float acc = 0.0f;
+                            for (int k = 0; k < 9; ++k) {
+                                const int hh = h + k / 3 - 1, ww = w + k % 3 - 1;
+                                float val = 0.0f;
+                                if (hh >= 0 && hh < H && ww >= 0 && ww < W)
+                                    val = RND(load_elem(field, (((int64_t)b * H + hh) * W + ww) * D + d, dt) * (float)f);
+                                acc += RND(p[k] * val);
+                            }
+                            store_elem(out, ((((int64_t)b * H * f + (int64_t)h * f + i) * W * f) + (int64_t)w * f + j) * D + d,
+                                       acc, dt);
+                        }
+                    }
     return 0;
 }

@@ -28,7 +28,24 @@ def ulp16(ref, dtype):
 
 
 def golden_names(pattern="*"):
-    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, pattern + ".npz")))
+    """Golden files of the operator (the upsample_* files belong to load_golden_upsample)."""
+    names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, pattern + ".npz")))
+    return [n for n in names if not n.startswith("upsample_")]
+
+
+def golden_upsample_names():
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "upsample_*.npz")))
+
+
+def load_golden_upsample(name):
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    dt = DTYPES[str(z["dtype"])]
+
+    def t(key):
+        a = torch.from_numpy(z[key].copy())
+        return a.view(torch.bfloat16) if dt == torch.bfloat16 else a
+
+    return dict(dtype=dt, factor=int(z["factor"]), field=t("field"), mask=t("mask"), out=t("out"))
 
 
 def load_golden(name):
@@ -79,6 +96,22 @@ def assert_close(got, ref, dtype, what="", ties=False):
             f"{what}: {over:.2e} of the elements exceed {ABS_TOL[dtype]} (worst {e:.2f}x) for {dtype}"
         return
     assert e <= 1.0, f"{what}: error is {e:.3f}x the allowed tolerance for {dtype}"
+
+
+def assert_close_sum_of_products(got, ref, dtype, term_scale, what=""):
+    """For outputs that are short sums of 16-bit products whose terms are much larger than the result
+    (the convex upsampling: nine products of magnitude up to `term_scale` that partly cancel): a last-bit
+    difference in one softmax weight moves one product by an ulp at the TERM's magnitude, so the bound is
+    two 16-bit ulps at `term_scale` instead of at the result.  float32 keeps the 1e-4 relative rule.
+    (Eager PyTorch itself differs between CPU and GPU at this level: its CPU softmax along a non-last
+    dimension is not the round-once-from-float32 result in about 10 % of the float16 elements.)"""
+    if dtype == torch.float32:
+        return assert_close(got, ref, dtype, what)
+    g, r = got.detach().cpu().float(), ref.detach().cpu().float()
+    assert torch.isfinite(g).all(), f"{what}: non-finite output"
+    allowed = max(ABS_TOL[dtype], 2.0 * float(ulp16(torch.tensor(float(term_scale)), dtype)))
+    worst = float((g - r).abs().max())
+    assert worst <= allowed, f"{what}: error {worst:.4g} exceeds {allowed:.4g} for {dtype}"
 
 
 def grid_xy(B, H, W, h, rows=None):

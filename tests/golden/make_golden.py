@@ -196,16 +196,38 @@ def model_cases(ref_root, impl):
                   f"call {last} of a MatchStereo-tiny forward at 192x192, torch seed 21, batch item 0, cast to f16")
 
 
+def upsample_cases(ref_root):
+    """MatchStereo.upsample_field (models/match_stereo.py:73-84) on seeded inputs, factors 2 and 4."""
+    from models.match_stereo import MatchStereo
+    for name, seed, B, H, W, D, factor in (("upsample_f2", 31, 2, 7, 9, 2, 2), ("upsample_f4", 32, 1, 6, 5, 2, 4),
+                                           ("upsample_f2_d8", 33, 1, 5, 6, 8, 2)):
+        gen = torch.Generator().manual_seed(seed)
+        field32 = torch.randn(B, H, W, D, generator=gen) * 3
+        mask32 = torch.randn(B, 9 * factor * factor, H, W, generator=gen) * 2
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            field, mask = field32.to(dtype), mask32.to(dtype)
+            out = MatchStereo.upsample_field(None, field, mask, factor)
+            tag = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[dtype]
+            path = os.path.join(HERE, f"{name}_{tag}.npz")
+            np.savez_compressed(path, dtype=str(dtype).replace("torch.", ""), factor=factor, field=to_np(field),
+                                mask=to_np(mask), out=to_np(out),
+                                note=f"seed {seed}, MatchStereo.upsample_field of the reference on CPU")
+            print(f"{name}_{tag}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF", "/root/reference"))
     ap.add_argument("--skip-model", action="store_true")
+    ap.add_argument("--only-upsample", action="store_true", help="regenerate only the upsample_field vectors")
     a = ap.parse_args()
     impl, blocks = import_reference(a.ref)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    synthetic_cases(impl, blocks)
-    if not a.skip_model:
-        model_cases(a.ref, impl)
+    if not a.only_upsample:
+        synthetic_cases(impl, blocks)
+        if not a.skip_model:
+            model_cases(a.ref, impl)
+    upsample_cases(a.ref)
 
 
 if __name__ == "__main__":
