@@ -401,6 +401,36 @@ def run_upsample_mode(args):
                                    "frac": nbytes / ms / 1e6 / peak, "peak_kind": kind}}), flush=True)
 
 
+def run_volume_mode(args):
+    """The stereo cost volume of GlobalCorrelation at 1/32 of 1536x1536 (48x48 tokens) and of 2176x3840
+    (68x120 tokens), float16: one kernel instead of the reference's loops over the disparities."""
+    import matchattention_b200 as ma
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows = []
+    for B, H, W in ((1, 48, 48), (1, 68, 120)):
+        corr = (torch.randn(B, H, W, W, device=dev) * 3).half()
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            ma.stereo_volume(corr)
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(10):
+                    vol = ma.stereo_volume(corr)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            graph.replay()
+        e0.record()
+        for _ in range(20):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        rows.append({"B": B, "H": H, "W": W, "us_per_call": e0.elapsed_time(e1) / 200 * 1000,
+                     "bytes": (corr.numel() + vol.numel()) * 2})
+    print(json.dumps({"metric": "stereo_volume_us", "value": rows[0]["us_per_call"], "unit": "us", "n_gpus": 1,
+                      "higher_is_better": False, "dtype": "f16", "data": "synthetic", "config": {"shapes": rows}}), flush=True)
+
+
 def config_dict(name, wl):
     return {"workload": name, "B_per_gpu": wl["B"], "token_map": [wl["H"], wl["W"]], "heads": wl["h"],
             "head_dim": wl["hd"], "win_r": wl["r"], "window_taps": (2 * wl["r"] + 2) ** 2,
@@ -416,7 +446,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--mode", choices=["pairs", "band", "model_ops", "upsample"], default="pairs",
+    ap.add_argument("--mode", choices=["pairs", "band", "model_ops", "upsample", "volume"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
     ap.add_argument("--band-kv", choices=["broadcast", "halo"], default="broadcast",
@@ -449,6 +479,9 @@ def main():
         return
     if args.mode == "upsample":
         run_upsample_mode(args)
+        return
+    if args.mode == "volume":
+        run_volume_mode(args)
         return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

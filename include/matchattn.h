@@ -211,6 +211,17 @@ MATCHATTN_API int matchattn_fused_forward_static(const void *max_offset, const v
 MATCHATTN_API int matchattn_upsample_field(const void *field, const void *mask, void *out,
                                            int B, int H, int W, int D, int factor, int dtype, void *cuda_stream);
 
+/*
+ * Cost volume of the stereo branch of GlobalCorrelation, the step before the first MatchAttention
+ * block (models/cost_volume.py:26-51: masks, the two Python loops over the disparities, the softmax
+ * over disparity and the out-of-view fill), as one kernel.
+ *   correlation [B, H, W, W]     scaled q.k^T of a row: reference column, then target column
+ *   volume      [2B, W, H, W]    written: left view in the first B items, right view in the last B
+ * W <= 159 (the row's W x W slice is staged in shared memory).  Allocates nothing.
+ */
+MATCHATTN_API int matchattn_stereo_volume(const void *correlation, void *volume, int B, int H, int W, int dtype,
+                                          void *cuda_stream);
+
 /* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */
 MATCHATTN_API const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned);

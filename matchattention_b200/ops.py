@@ -268,3 +268,24 @@ def upsample_field(field: torch.Tensor, mask: torch.Tensor, factor: int) -> torc
                                                    torch.cuda.current_stream().cuda_stream)
     _lib.check(status)
     return out
+
+
+def stereo_volume(correlation: torch.Tensor) -> torch.Tensor:
+    """The cost volume GlobalCorrelation builds from its row-wise correlation in the stereo branch
+    (models/cost_volume.py:26-51): correlation [B,H,W,W] -> volume [2B,W,H,W] (softmaxed over the
+    disparity axis, out-of-view columns filled), one kernel instead of the loops over disparities."""
+    if not correlation.is_cuda:
+        raise RuntimeError("matchattn_b200 runs on CUDA tensors only (no CPU fallback); got device "
+                           + str(correlation.device))
+    if correlation.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {correlation.dtype}")
+    if correlation.dim() != 4 or correlation.size(2) != correlation.size(3):
+        raise ValueError("expected correlation [B,H,W,W]")
+    corr = correlation.contiguous()
+    B, H, W, _ = corr.shape
+    vol = corr.new_empty(2 * B, W, H, W)
+    with torch.cuda.device(corr.device):
+        status = _lib.lib.matchattn_stereo_volume(corr.data_ptr(), vol.data_ptr(), B, H, W, _DTYPE_CODE[corr.dtype],
+                                                  torch.cuda.current_stream().cuda_stream)
+    _lib.check(status)
+    return vol

@@ -369,3 +369,54 @@ int matchattn_oracle_upsample_field(const void *field, const void *mask, void *o
                     }
     return 0;
 }
+
+/*
+ * Cost volume of the stereo branch of GlobalCorrelation (models/cost_volume.py:26-51), from the
+ * correlation [B, H, W, W] (reference index, then target index along a row) to the volume
+ * [2B, D = W, H, W] the module returns:
+ *   first half  (left view):   vol[b, d, h, w]   = corr[b, h, w, w - d]   for w >= d, else 0
+ *   second half (right view):  vol[B+b, d, h, w] = corr[b, h, w + d, w]   for w + d < W, else 0
+ * (the positions the reference masks with -1e9 / -1e4 are exactly the ones these shifts never read),
+ * then a softmax over d, rounded to the tensor type, and the out-of-view fill: the left view copies
+ * column d into columns w < d, the right view copies column W-1-d into columns w > W-1-d.
+ */
+int matchattn_oracle_stereo_volume(const void *corr, void *volume, int B, int H, int W, int dtype)
+{
+    if (!corr || !volume) return 1;
+    if (B <= 0 || H <= 0 || W <= 0) return 2;
+    if (dtype != MA_F32 && dtype != MA_F16 && dtype != MA_BF16) return 4;
+    ensure_half_table();
+    const int dt = dtype, D = W;
+    float *sm = (float *)malloc(sizeof(float) * (size_t)D * W);
+    if (!sm) return 2;
+    for (int b2 = 0; b2 < 2 * B; ++b2)
+        for (int h = 0; h < H; ++h) {
+            const int right = b2 >= B, b = right ? b2 - B : b2;
+            const int64_t row = ((int64_t)b * H + h) * W * W;          /* corr[b, h, :, :] */
+            for (int w = 0; w < W; ++w) {
+                float mx = -INFINITY, den = 0.0f;
+                for (int d = 0; d < D; ++d) {
+                    float val = 0.0f;
+                    if (!right && w >= d) val = load_elem(corr, row + (int64_t)w * W + (w - d), dt);
+                    if (right && w + d < W) val = load_elem(corr, row + (int64_t)(w + d) * W + w, dt);
+                    sm[(size_t)d * W + w] = val;
+                    mx = val > mx ? val : mx;
+                }
+                for (int d = 0; d < D; ++d) {
+                    const float e = expf(sm[(size_t)d * W + w] - mx);
+                    sm[(size_t)d * W + w] = e;
+                    den += e;
+                }
+                for (int d = 0; d < D; ++d) sm[(size_t)d * W + w] = RND(sm[(size_t)d * W + w] / den);
+            }
+            for (int d = 0; d < D; ++d)
+                for (int w = 0; w < W; ++w) {
+                    int src = w;
+                    if (!right && w < d) src = d;
+                    if (right && w > W - 1 - d) src = W - 1 - d;
+                    store_elem(volume, (((int64_t)b2 * D + d) * H + h) * W + w, sm[(size_t)d * W + src], dt);
+                }
+        }
+    free(sm);
+    return 0;
+}

@@ -30,11 +30,26 @@ def ulp16(ref, dtype):
 def golden_names(pattern="*"):
     """Golden files of the operator (the upsample_* files belong to load_golden_upsample)."""
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, pattern + ".npz")))
-    return [n for n in names if not n.startswith("upsample_")]
+    return [n for n in names if not n.startswith(("upsample_", "volume_"))]
 
 
 def golden_upsample_names():
     return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "upsample_*.npz")))
+
+
+def golden_volume_names():
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "volume_*.npz")))
+
+
+def load_golden_volume(name):
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    dt = DTYPES[str(z["dtype"])]
+
+    def t(key):
+        a = torch.from_numpy(z[key].copy())
+        return a.view(torch.bfloat16) if dt == torch.bfloat16 else a
+
+    return dict(dtype=dt, correlation=t("correlation"), volume=t("volume"))
 
 
 def load_golden_upsample(name):

@@ -215,6 +215,31 @@ def upsample_cases(ref_root):
             print(f"{name}_{tag}: {os.path.getsize(path) / 1024:.0f} KiB")
 
 
+def volume_cases(ref_root):
+    """GlobalCorrelation.forward, stereo branch (models/cost_volume.py:17-55): the correlation the module
+    computes from its input (lines 18-24, recomputed here with the module's own layers) and the cost volume
+    it returns (lines 26-51: masking, diagonal shifts, softmax over disparity, out-of-view fill)."""
+    from models.cost_volume import GlobalCorrelation
+    for name, seed, B, H, W, C in (("volume_w12", 41, 1, 5, 12, 16), ("volume_w20", 42, 2, 3, 20, 8)):
+        torch.manual_seed(seed)
+        mod = GlobalCorrelation(C).eval()
+        x32 = torch.randn(2 * B, H, W, C) * 2
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            m = mod.to(dtype)
+            x = x32.to(dtype)
+            with torch.inference_mode():
+                xn = m.norm(x)
+                ref, tgt = xn.chunk(2, dim=0)
+                corr = torch.matmul(m.q(ref), m.k(tgt).transpose(-2, -1)) * m.scale
+                _, volume = m(x, stereo=True)
+            tag = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[dtype]
+            path = os.path.join(HERE, f"{name}_{tag}.npz")
+            np.savez_compressed(path, dtype=str(dtype).replace("torch.", ""), correlation=to_np(corr.contiguous()),
+                                volume=to_np(volume.contiguous()),
+                                note=f"seed {seed}, GlobalCorrelation(dim={C}) of the reference on CPU, stereo=True")
+            print(f"{name}_{tag}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF", "/root/reference"))
@@ -223,11 +248,12 @@ def main():
     a = ap.parse_args()
     impl, blocks = import_reference(a.ref)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    if not a.only_upsample:
+    if not a.only_upsample:   # (the flag also regenerates the cost-volume vectors)
         synthetic_cases(impl, blocks)
         if not a.skip_model:
             model_cases(a.ref, impl)
     upsample_cases(a.ref)
+    volume_cases(a.ref)
 
 
 if __name__ == "__main__":
