@@ -179,12 +179,13 @@ struct DT<__half> {
         x = f.x;
         y = f.y;
     }
-    static __device__ __forceinline__ void absdiff(float &a0, float &, uint32_t qw, uint32_t kw)
+    static __device__ __forceinline__ void absdiff(float &a0, float &a1, uint32_t qw, uint32_t kw)
     {
-        // the difference is rounded to float16 (as the reference does), its magnitude is added in float32
-        const __half2 d = __hsub2(*reinterpret_cast<const __half2 *>(&qw), *reinterpret_cast<const __half2 *>(&kw));
-        const float2 f = __half22float2(d);
-        a0 += fabsf(f.x) + fabsf(f.y);
+        // the difference is rounded to float16 (as the reference does); its magnitude is added to the
+        // float32 sums with the mixed-precision add (two chains, even and odd channels)
+        const __half2 d = __habs2(__hsub2(*reinterpret_cast<const __half2 *>(&qw), *reinterpret_cast<const __half2 *>(&kw)));
+        a0 = add_f32_f16(a0, __half_as_ushort(__low2half(d)));
+        a1 = add_f32_f16(a1, __half_as_ushort(__high2half(d)));
     }
     using Bcast = __half2;
     static __device__ __forceinline__ Bcast bcast(__half a) { return __half2half2(a); }
