@@ -33,6 +33,7 @@ WORKLOADS = {
     # name: B, H, W, h, hd, r, dtype, kind, spread (tokens), border_frac, per_head
     "op_384x384_b4_h8x16_r1_f16_flow": (4, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, False),
     "op_384x384_b4_h8x16_r1_f32_flow": (4, 384, 384, 8, 16, 1, torch.float32, "flow", 24.0, 0.1, False),
+    "op_384x384_b4_h8x16_r1_bf16_flow": (4, 384, 384, 8, 16, 1, torch.bfloat16, "flow", 24.0, 0.1, False),
     "op_384x384_b4_h8x16_r1_f16_flow_perhead": (4, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, True),
     "op_384x384_b4_h8x16_r1_f16_smooth": (4, 384, 384, 8, 16, 1, torch.float16, "self", 3.0, 0.0, True),
     "op_384x384_b1_h8x16_r1_f16_flow": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, False),

@@ -29,7 +29,10 @@
 
 namespace matchattn {
 
-constexpr int kThreads = 256;
+#ifndef MATCHATTN_THREADS
+#define MATCHATTN_THREADS 256
+#endif
+constexpr int kThreads = MATCHATTN_THREADS;
 
 struct Params {
     const void *mo, *q, *k, *v;
@@ -122,10 +125,23 @@ __device__ __forceinline__ void store_words(void *p, const uint32_t (&w)[NW])
     }
 }
 
+// row pointer + unsigned byte offset (one widening multiply-add instead of a 64-bit add with carry)
+template <typename T>
+__device__ __forceinline__ const T *tap_ptr(const T *row, uint32_t byte_off)
+{
+    return reinterpret_cast<const T *>(reinterpret_cast<const char *>(row) + byte_off);
+}
+
 // float32 accumulator += float16 addend in one instruction (PTX ISA 8.6, sm_100+)
 __device__ __forceinline__ float add_f32_f16(float acc, unsigned short h)
 {
     asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc) : "h"(h));
+    return acc;
+}
+
+__device__ __forceinline__ float add_f32_bf16(float acc, unsigned short h)
+{
+    asm("add.rn.f32.bf16 %0, %1, %0;" : "+f"(acc) : "h"(h));
     return acc;
 }
 
@@ -170,7 +186,7 @@ template <>
 struct DT<__half> {
     static constexpr int kWordsPerChunk = 4;   // 8 channels * 2 bytes
     static constexpr int kElemsPerWord = 2;
-    static constexpr bool kHalfPipe = true;    // float16 arithmetic needs few enough registers for 3 blocks per SM
+    static constexpr bool kHalfPipe = true;    // 16-bit arithmetic needs few enough registers for 3 blocks per SM
     static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); }
     static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
     {
@@ -240,7 +256,7 @@ template <>
 struct DT<__nv_bfloat16> {
     static constexpr int kWordsPerChunk = 4;
     static constexpr int kElemsPerWord = 2;
-    static constexpr bool kHalfPipe = false;
+    static constexpr bool kHalfPipe = true;
     static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
     static __device__ __forceinline__ void load_xy(const void *p, float &x, float &y)
     {
@@ -252,9 +268,9 @@ struct DT<__nv_bfloat16> {
     {
         const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&qw),
                                          *reinterpret_cast<const __nv_bfloat162 *>(&kw));
-        const uint32_t u = *reinterpret_cast<const uint32_t *>(&d);
-        a0 += fabsf(__uint_as_float(u << 16));
-        a1 += fabsf(__uint_as_float(u & 0xffff0000u));
+        const uint32_t u = *reinterpret_cast<const uint32_t *>(&d) & 0x7fff7fffu;
+        a0 = add_f32_bf16(a0, static_cast<unsigned short>(u & 0xffffu));
+        a1 = add_f32_bf16(a1, static_cast<unsigned short>(u >> 16));
     }
     using Bcast = __nv_bfloat162;
     static __device__ __forceinline__ Bcast bcast(__nv_bfloat16 a) { return __bfloat162bfloat162(a); }
@@ -262,8 +278,8 @@ struct DT<__nv_bfloat16> {
     {
         const __nv_bfloat162 t = __hmul2_rn(a, *reinterpret_cast<const __nv_bfloat162 *>(&vw));
         const uint32_t u = *reinterpret_cast<const uint32_t *>(&t);
-        o[0] += __uint_as_float(u << 16);
-        o[1] += __uint_as_float(u & 0xffff0000u);
+        o[0] = add_f32_bf16(o[0], static_cast<unsigned short>(u & 0xffffu));
+        o[1] = add_f32_bf16(o[1], static_cast<unsigned short>(u >> 16));
     }
     static __device__ __forceinline__ uint32_t pack(const float *o)
     {
@@ -471,7 +487,11 @@ template <typename T, int R, int CPL>
 constexpr int min_blocks()
 {
     if (R != 1) return 1;
+#ifdef MATCHATTN_MINB
+    return (DT<T>::kHalfPipe && CPL <= 2) ? MATCHATTN_MINB : 2 * (256 / kThreads);
+#else
     return (DT<T>::kHalfPipe && CPL <= 2) ? 3 : 2;
+#endif
 }
 
 // EXTRAS selects the build of the kernel that also honours the rarely used Params fields (sorted
@@ -544,10 +564,12 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     float wgt[4];
     bilinear_weights<T>(x, xf, y, yf, wgt);
     const int x0 = window_origin(xf, R, p.W) - R, y0 = window_origin(yf, R, p.H) - R;
-    int col[SIDE], row[SIDE];
+    // a tap's address is its row's pointer plus an unsigned 32-bit byte offset of its column
+    uint32_t col[SIDE];
+    int row[SIDE];
 #pragma unroll
     for (int i = 0; i < SIDE; ++i) {
-        col[i] = min(max(x0 + i, 0), p.W - 1) * p.C;
+        col[i] = static_cast<uint32_t>(min(max(x0 + i, 0), p.W - 1) * p.C) * static_cast<uint32_t>(sizeof(T));
         row[i] = min(max(y0 + i, 0), p.H - 1) * p.W * p.C;
     }
 
@@ -566,7 +588,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
 #pragma unroll
         for (int i = 0; i < SIDE; ++i) {
             uint32_t kw[NW];
-            load_words<NW>(kw, kb + (row[j] + col[i]));
+            load_words<NW>(kw, tap_ptr(kb + row[j], col[i]));
             float a0 = 0.f, a1 = 0.f;
 #pragma unroll
             for (int w = 0; w < NW; ++w) {
@@ -579,6 +601,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
             }
             s[j * SIDE + i] = finish_score<T>(part, p.scale);
         }
+
+    // the first value taps are requested before the softmax so that their latency overlaps it
+    // (two taps: measured best, more of them spill)
+    constexpr int VPF = (R == 1 && CPL <= 2) ? 2 : 0;
+    uint32_t vpre[VPF > 0 ? VPF : 1][NW];
+#pragma unroll
+    for (int t = 0; t < VPF; ++t) load_words<NW>(vpre[t], tap_ptr(vb + row[t / SIDE], col[t % SIDE]));
 
     constexpr int NWA = M / EPW;
     uint32_t aw[NWA];
@@ -596,7 +625,12 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
 #pragma unroll
         for (int i = 0; i < SIDE; ++i) {
             uint32_t vw[NW];
-            load_words<NW>(vw, vb + (row[j] + col[i]));
+            if (j * SIDE + i < VPF) {
+#pragma unroll
+                for (int w = 0; w < NW; ++w) vw[w] = vpre[j * SIDE + i][w];
+            } else {
+                load_words<NW>(vw, tap_ptr(vb + row[j], col[i]));
+            }
             const typename DT<T>::Bcast am = DT<T>::aw_tap(aw, j * SIDE + i);
 #pragma unroll
             for (int w = 0; w < NW; ++w) DT<T>::wmul(am, vw[w], &o[w * EPW]);

@@ -242,7 +242,8 @@ def volume_cases(ref_root):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF"), required="MATCHATTN_REF" not in os.environ,
+                    help="checkout of the reference project (or set MATCHATTN_REF)")
     ap.add_argument("--skip-model", action="store_true")
     ap.add_argument("--only-upsample", action="store_true", help="regenerate only the upsample_field vectors")
     a = ap.parse_args()
