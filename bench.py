@@ -61,11 +61,11 @@ def measured_peak():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries
-# (profiles/fused_forward_f16_cpl2_op_384x384_b1.md: 169.3 MB for the one-item case; traffic is
+# (profiles/fused_forward_f16_cpl2_op_384x384_b1.md: 168.9 MB for the one-item case; traffic is
 # proportional to the items of a launch, so the four-item bench launch moves four times that)
 NCU_TRAFFIC_BYTES = {
-    "op_384x384_b1_h8x16_r1_f16_flow": 169.3e6,
-    "op_384x384_b4_h8x16_r1_f16_flow": 4 * 169.3e6,
+    "op_384x384_b1_h8x16_r1_f16_flow": 168.9e6,
+    "op_384x384_b4_h8x16_r1_f16_flow": 4 * 168.9e6,
 }
 
 

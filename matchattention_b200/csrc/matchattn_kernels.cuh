@@ -29,10 +29,7 @@
 
 namespace matchattn {
 
-#ifndef MATCHATTN_THREADS
-#define MATCHATTN_THREADS 256
-#endif
-constexpr int kThreads = MATCHATTN_THREADS;
+constexpr int kThreads = 256;
 
 struct Params {
     const void *mo, *q, *k, *v;
@@ -487,11 +484,7 @@ template <typename T, int R, int CPL>
 constexpr int min_blocks()
 {
     if (R != 1) return 1;
-#ifdef MATCHATTN_MINB
-    return (DT<T>::kHalfPipe && CPL <= 2) ? MATCHATTN_MINB : 2 * (256 / kThreads);
-#else
     return (DT<T>::kHalfPipe && CPL <= 2) ? 3 : 2;
-#endif
 }
 
 // EXTRAS selects the build of the kernel that also honours the rarely used Params fields (sorted
