@@ -38,6 +38,8 @@ WORKLOADS = {
     "op_384x384_b4_h8x16_r1_f16_smooth": (4, 384, 384, 8, 16, 1, torch.float16, "self", 3.0, 0.0, True),
     "op_384x384_b1_h8x16_r1_f16_flow": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, False),
     "op_384x384_b1_h8x16_r1_f16_smooth": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 3.0, 0.0, False),
+    "op_96x96_b2_h4x32_r2_f16_self": (2, 96, 96, 4, 32, 2, torch.float16, "self", 3.0, 0.0, True),      # 1/16 stage of MatchStereo-T
+    "op_48x48_b2_h4x40_r2_f16_self": (2, 48, 48, 4, 40, 2, torch.float16, "self", 3.0, 0.0, True),      # 1/32 stage
     "op_104x208_b1_h8x16_r1_f32_cross": (1, 104, 208, 8, 16, 1, torch.float32, "cross", 16.0, 0.0, False),
 }
 DEFAULT_WORKLOAD = "op_384x384_b4_h8x16_r1_f16_flow"
@@ -335,9 +337,12 @@ def run_model_ops_mode(args):
             calls.append((cross, q, k, v, out, attn, side, r, hd))
             alg_bytes += 2 * B * N * (4 * C + 2 * h) + 2 * B * N * (4 * C + 2 * h + h * M)
 
+    def knobs_of(r):     # --variant / --chunks-per-lane apply to the r = 2 calls (kernel experiments)
+        return dict(variant=args.variant, chunks_per_lane=args.chunks_per_lane) if r == 2 else {}
+
     def forward_ops():
         for mo, q, k, v, out, attn, side, r, hd in calls:
-            ma.launch(mo, q, k, v, out, attn, side, side, (r, r), "l1_norm", hd ** -0.5)
+            ma.launch(mo, q, k, v, out, attn, side, side, (r, r), "l1_norm", hd ** -0.5, **knobs_of(r))
 
     def timed(fn, n):
         for _ in range(max(3, args.warmup)):
@@ -353,6 +358,22 @@ def run_model_ops_mode(args):
 
     n = max(5, min(args.steps, 100))
     eager_ms = timed(forward_ops, n)
+    # one call of each distinct kind on its own (the layers of a stage repeat it)
+    per_call = []
+    for idx in sorted({(c[6], c[5] is None): i for i, c in enumerate(calls)}.values()):
+        mo, q, k, v, out, attn, side, r, hd = calls[idx]
+        def twenty():
+            for _ in range(20):
+                ma.launch(mo, q, k, v, out, attn, side, side, (r, r), "l1_norm", hd ** -0.5, **knobs_of(r))
+        # as a CUDA graph of 20 launches: the small calls take less device time than a launch takes the host
+        g20, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            twenty()
+            with torch.cuda.graph(g20, stream=st):
+                twenty()
+        torch.cuda.synchronize()
+        us = 1e3 * timed(g20.replay, 20) / 20
+        per_call.append({"side": side, "r": r, "hd": hd, "kind": "self" if attn is None else "cross", "us": round(us, 2)})
     graph = torch.cuda.CUDAGraph()
     side_stream = torch.cuda.Stream()
     with torch.cuda.stream(side_stream):
@@ -366,7 +387,8 @@ def run_model_ops_mode(args):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "52 MatchAttention calls of MatchStereo-T at 1536x1536 (B=2, h=4)",
                        "stages_side_C_r_layers": stages, "eager_ms": eager_ms, "cuda_graph_ms": graph_ms,
-                       "algorithmic_bytes": alg_bytes, "algorithmic_GBps_graph": alg_bytes / graph_ms / 1e6},
+                       "algorithmic_bytes": alg_bytes, "algorithmic_GBps_graph": alg_bytes / graph_ms / 1e6,
+                       "per_call_us_in_a_graph_of_20": per_call},
             "gpu_launches": 52 * n}
     print(json.dumps(line), flush=True)
 
@@ -433,9 +455,13 @@ def run_volume_mode(args):
 
 
 def config_dict(name, wl):
+    step_mb = wl["B"] * wl["H"] * wl["W"] * algorithmic_bytes_per_query(wl["h"], wl["hd"], wl["r"],
+                                                                        torch.empty(0, dtype=wl["dtype"]).element_size()) / 1e6
+    l2 = "inputs+outputs of one step exceed the 126 MB L2; no flush between steps" if step_mb > 126 else \
+         f"inputs+outputs of one step ({step_mb:.0f} MB) fit the 126 MB L2 and stay resident between steps, as they " \
+         "do between the layers of the model; not a bandwidth measurement"
     return {"workload": name, "B_per_gpu": wl["B"], "token_map": [wl["H"], wl["W"]], "heads": wl["h"],
-            "head_dim": wl["hd"], "win_r": wl["r"], "window_taps": (2 * wl["r"] + 2) ** 2,
-            "l2": "inputs+outputs of one step exceed the 126 MB L2; no flush between steps"}
+            "head_dim": wl["hd"], "win_r": wl["r"], "window_taps": (2 * wl["r"] + 2) ** 2, "l2": l2}
 
 
 def main():
@@ -456,7 +482,8 @@ def main():
                     help="band mode: q / max_offset / outputs stay distributed, only K/V move each step")
     ap.add_argument("--tile-w", type=int, default=0)
     ap.add_argument("--chunks-per-lane", type=int, default=0)
-    ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 scalar kernel, 2 matrix-instruction kernel")
+    ap.add_argument("--no-graph", action="store_true", help="time K plain launches instead of one graph of K launches")
+    ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 scalar kernel, 2/3 matrix-instruction kernels")
     ap.add_argument("--strategy", type=int, default=0, help="0 auto, 1 direct kernel, 2 binned path")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -514,15 +541,30 @@ def main():
     if sampler:
         sampler.start()
 
-    # ---- device-resident timing: exactly K steps between two events on the launching stream
+    # ---- device-resident timing: exactly K steps between two events on the launching stream.
+    # The K launches are replayed as one CUDA graph so that the small workloads, whose kernel takes
+    # less device time than a launch takes the host, are timed on the device too (--no-graph: plain launches).
     for _ in range(args.warmup):
         step()
     barrier()
+    run_steps = None
+    if not args.no_graph:
+        graph, cap = torch.cuda.CUDAGraph(), torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(cap):
+            step()
+            with torch.cuda.graph(graph, stream=cap):
+                for _ in range(args.steps):
+                    step()
+        run_steps = graph.replay
+        barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.perf_counter()
     ev0.record()
-    for _ in range(args.steps):
-        step()
+    if run_steps is not None:
+        run_steps()
+    else:
+        for _ in range(args.steps):
+            step()
     ev1.record()
     barrier()
     t_wall1 = time.perf_counter()

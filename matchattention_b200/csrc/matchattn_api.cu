@@ -213,6 +213,8 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     // index ranges the kernels rely on: per-item offsets in 32 bits, batch on grid.y
     if (C > 65536 || N * C >= 2147483647LL || Nq * h * M >= 2147483647LL || B > 65535) return MATCHATTN_ERR_TOO_LARGE;
     const uintptr_t esize = dtype == MATCHATTN_F32 ? 4 : 2;
+    // a tap's column is an unsigned 32-bit byte offset within its row
+    if (1LL * W * C * static_cast<long long>(esize) >= (1LL << 32)) return MATCHATTN_ERR_TOO_LARGE;
     const long long out_stride = glue.out_stride > 0 ? glue.out_stride : C;
     const long long attn_stride = glue.attn_stride > 0 ? glue.attn_stride : 1LL * h * M;
     if (out_stride < C || attn_stride < 1LL * h * M || out_stride >= (1LL << 30) || attn_stride >= (1LL << 30))

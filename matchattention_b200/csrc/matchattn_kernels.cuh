@@ -483,7 +483,9 @@ __device__ __forceinline__ void bilinear_softmax(const float (&s)[(2 * R + 2) * 
 template <typename T, int R, int CPL>
 constexpr int min_blocks()
 {
-    if (R != 1) return 1;
+    // r = 2 holds a 36-tap window per lane: one block per SM without a register limit, two (128
+    // registers, a few spilled words) for the 16-bit types up to four chunks per lane
+    if (R != 1) return (DT<T>::kHalfPipe && CPL <= 4) ? 2 : 1;
     return (DT<T>::kHalfPipe && CPL <= 2) ? 3 : 2;
 }
 
