@@ -91,7 +91,9 @@ Plan make_plan(int h, int hd, int r, int cpl_request)
         if (cpl_request > 5 || hd8 % cpl_request != 0 || !is_pow2(hd8 / cpl_request)) return pl;
         cpl = cpl_request;
     } else {
-        while (cpl * 2 <= 4 && hd8 % (cpl * 2) == 0) cpl *= 2;
+        // r = 2 keeps a 36-tap window per lane: narrower slices (more lanes per head) leave room for it
+        const int cap = r == 2 ? 2 : 4;
+        while (cpl * 2 <= cap && hd8 % (cpl * 2) == 0) cpl *= 2;
     }
     const int lph = hd8 / cpl;
     if (lph > 32 || h * lph > kThreads) return pl;
