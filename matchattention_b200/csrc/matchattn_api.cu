@@ -103,6 +103,15 @@ Plan make_plan(int h, int hd, int r, int cpl_request)
     return pl;
 }
 
+// SMs of the current device (148 when the query fails)
+inline int sm_count()
+{
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return 148;
+    return sms > 0 ? sms : 148;
+}
+
 inline bool aligned(const void *p, uintptr_t a) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // The matrix-instruction kernel: unsorted (walks the map in tiles) or in sorted order.  In sorted
@@ -152,25 +161,35 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
             err = run_mma<T>(p, pl.cpl, p.sorted != nullptr ? p.guard : nullptr, pl.mma_nch, stream);
             return err == cudaSuccess ? MATCHATTN_OK : MATCHATTN_ERR_CUDA + static_cast<int>(err);
         }
-        const int qpb = kThreads / p.G;              // queries per block (>= 1)
-        const int qpw = p.G >= 32 ? 1 : 32 / p.G;    // queries a warp covers, kept in one row
-        int tw;
-        if (tile_w_request > 0) {
-            tw = 1;
-            while (tw * 2 <= tile_w_request && tw * 2 <= qpb) tw *= 2;
-        } else {
-            tw = 1;
-            while (tw * tw < qpb) tw *= 2;           // about square
-            if (tw < qpw) tw = qpw;
+        int threads = kThreads;
+        long long blocks = 0;
+        const long long fill = 2LL * sm_count();
+        for (;;) {
+            const int qpb = threads / p.G;               // queries per block (>= 1)
+            const int qpw = p.G >= 32 ? 1 : 32 / p.G;    // queries a warp covers, kept in one row
+            int tw;
+            if (tile_w_request > 0) {
+                tw = 1;
+                while (tw * 2 <= tile_w_request && tw * 2 <= qpb) tw *= 2;
+            } else {
+                tw = 1;
+                while (tw * tw < qpb) tw *= 2;           // about square
+                while (tw * 2 <= qpw) tw *= 2;       // at least a warp's queries wide, as a power of two
+            }
+            while (tw > qpb) tw >>= 1;
+            if (tw < 1) tw = 1;
+            p.tile_w = tw;
+            p.tile_w_shift = ilog2(tw);
+            p.tile_h = qpb / tw;
+            p.tiles_x = (p.W + p.tile_w - 1) / p.tile_w;
+            const int tiles_y = (p.rows + p.tile_h - 1) / p.tile_h;
+            blocks = 1LL * p.tiles_x * tiles_y;
+            // A launch too small to give every SM two blocks is bound by the latency of one warp's
+            // chain of taps: narrower blocks (the kernels only bound their size from above) spread
+            // the same queries over more SMs.
+            if (threads <= 64 || threads / 2 < p.G || blocks * p.B >= fill) break;
+            threads /= 2;
         }
-        while (tw > qpb) tw >>= 1;
-        if (tw < 1) tw = 1;
-        p.tile_w = tw;
-        p.tile_w_shift = ilog2(tw);
-        p.tile_h = qpb / tw;
-        p.tiles_x = (p.W + p.tile_w - 1) / p.tile_w;
-        const int tiles_y = (p.rows + p.tile_h - 1) / p.tile_h;
-        long long blocks = 1LL * p.tiles_x * tiles_y;
         unsigned grid_y = p.B;
         if (p.sorted != nullptr) {       // one flat list of queries over all batch items
             const long long per_block = 1LL * p.tile_w * p.tile_h;
@@ -179,7 +198,7 @@ int run(Params &p, const Plan &pl, int r, int tile_w_request, cudaStream_t strea
         }
         if (blocks > 2147483647LL) return MATCHATTN_ERR_TOO_LARGE;
         const dim3 grid(static_cast<unsigned>(blocks), grid_y);
-        err = launch_fast<T>(p, r, pl.cpl, pl.lph > 1, grid, stream);
+        err = launch_fast<T>(p, r, pl.cpl, pl.lph > 1, grid, threads, stream);
     } else {
         const long long per_item = 1LL * p.Nq * p.h;
         const long long blocks = (per_item + kThreads - 1) / kThreads;

@@ -752,7 +752,7 @@ __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params 
 
 // Launchers, one translation unit per element type.
 template <typename T>
-cudaError_t launch_fast(const Params &p, int r, int cpl, bool multi, dim3 grid, cudaStream_t stream);
+cudaError_t launch_fast(const Params &p, int r, int cpl, bool multi, dim3 grid, int threads, cudaStream_t stream);
 template <typename T>
 cudaError_t launch_generic(const Params &p, dim3 grid, cudaStream_t stream);
 

@@ -9,14 +9,14 @@
 namespace matchattn {
 
 template <typename T, int R>
-static cudaError_t launch_fast_r(const Params &p, int cpl, bool multi, dim3 grid, cudaStream_t stream)
+static cudaError_t launch_fast_r(const Params &p, int cpl, bool multi, dim3 grid, int threads, cudaStream_t stream)
 {
     const bool extras = p.guard != nullptr || p.sorted != nullptr || p.gate != nullptr || p.clamp != 0 ||
                         p.out_stride != p.C || p.attn_stride != p.h * (2 * R + 2) * (2 * R + 2);
 #define MA_CASE(CPL_, MULTI_)                                                              \
     if (cpl == CPL_ && multi == MULTI_) {                                                  \
-        if (extras) fused_forward_kernel<T, R, CPL_, MULTI_, true><<<grid, kThreads, 0, stream>>>(p);   \
-        else fused_forward_kernel<T, R, CPL_, MULTI_, false><<<grid, kThreads, 0, stream>>>(p);         \
+        if (extras) fused_forward_kernel<T, R, CPL_, MULTI_, true><<<grid, threads, 0, stream>>>(p);   \
+        else fused_forward_kernel<T, R, CPL_, MULTI_, false><<<grid, threads, 0, stream>>>(p);         \
         return cudaGetLastError();                                                         \
     }
     MA_CASE(1, false) MA_CASE(1, true)
@@ -29,10 +29,10 @@ static cudaError_t launch_fast_r(const Params &p, int cpl, bool multi, dim3 grid
 }
 
 template <>
-cudaError_t launch_fast<MATCHATTN_T>(const Params &p, int r, int cpl, bool multi, dim3 grid, cudaStream_t stream)
+cudaError_t launch_fast<MATCHATTN_T>(const Params &p, int r, int cpl, bool multi, dim3 grid, int threads, cudaStream_t stream)
 {
-    if (r == 1) return launch_fast_r<MATCHATTN_T, 1>(p, cpl, multi, grid, stream);
-    if (r == 2) return launch_fast_r<MATCHATTN_T, 2>(p, cpl, multi, grid, stream);
+    if (r == 1) return launch_fast_r<MATCHATTN_T, 1>(p, cpl, multi, grid, threads, stream);
+    if (r == 2) return launch_fast_r<MATCHATTN_T, 2>(p, cpl, multi, grid, threads, stream);
     return cudaErrorInvalidValue;
 }
 

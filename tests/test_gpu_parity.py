@@ -116,6 +116,22 @@ def test_variants_agree_bitwise_in_float16():
     assert attn is None and torch.equal(out, base_out)
 
 
+@pytest.mark.parametrize("r", [1, 2])
+@pytest.mark.parametrize("h,hd", [(1, 8), (3, 8), (5, 16), (6, 8), (7, 24), (3, 40)])
+def test_launch_geometry_of_small_maps(h, hd, r):
+    """Small launches run in narrower blocks, and a query's lanes need not divide a warp: whatever tile the
+    library picks, the result is the one of one-query-wide tiles, bit for bit, and matches the oracle."""
+    for H, W in ((7, 9), (13, 6), (21, 33)):
+        inputs = make_inputs(300 + 7 * h + H, 2, H, W, h, hd, r, torch.float16, kind="flow", spread=3.0, border_frac=0.2,
+                             per_head=True)
+        out, attn = run_kernel(inputs, H, W, r, hd ** -0.5)
+        out1, attn1 = run_kernel(inputs, H, W, r, hd ** -0.5, tile_w=1)
+        assert torch.equal(out, out1) and torch.equal(attn, attn1), (H, W)
+        ref_out, ref_attn = _oracle().forward(*inputs, H, W, r, hd ** -0.5)
+        assert_close(attn, ref_attn, torch.float16, f"attn {H}x{W}", ties=hd > 16)
+        assert_close(out, ref_out, torch.float16, f"out {H}x{W}", ties=hd > 16)
+
+
 def test_properties_at_full_size():
     """Size-independent checks on the headline shape: weights sum to one, identical offsets across heads give
     the same result as a per-head run, and shifting the whole problem by one token shifts the result."""
