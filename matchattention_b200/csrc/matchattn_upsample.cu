@@ -76,6 +76,25 @@ __global__ void __launch_bounds__(128) upsample_field_kernel(const T *__restrict
     }
 }
 
+// 2^x by the special-function unit (the weights are rounded to the tensor type right after)
+__device__ __forceinline__ float exp2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// a packed 32-bit word of two 16-bit values as the pair type of the element-wise helpers
+template <typename T>
+__device__ __forceinline__ typename DT<T>::Bcast word_as_pair(uint32_t w);
+template <>
+__device__ __forceinline__ float word_as_pair<float>(uint32_t w) { return __uint_as_float(w); }
+template <>
+__device__ __forceinline__ __half2 word_as_pair<__half>(uint32_t w) { return *reinterpret_cast<const __half2 *>(&w); }
+template <>
+__device__ __forceinline__ __nv_bfloat162 word_as_pair<__nv_bfloat16>(uint32_t w) { return *reinterpret_cast<const __nv_bfloat162 *>(&w); }
+
+
 // Vector path for the shapes the model uses (F*D <= 8, W a multiple of VW = 4): one thread owns four
 // consecutive coarse cells of one row h and ONE fine row i.  Its mask reads are 8- or 16-byte loads (four
 // cells of one channel), and the 4*f fine cells it produces are one contiguous run of 4*F*D elements of the
@@ -110,6 +129,14 @@ __global__ void __launch_bounds__(128) upsample_field_vec_kernel(const T *__rest
         }
     }
 
+    [[maybe_unused]] uint32_t nbw[3][VW + 2];
+    if constexpr (EPW == 2 && D == 2) {
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+            for (int c = 0; c < VW + 2; ++c) nbw[ky][c] = DT<T>::aw_from(nb[ky][c][0], nb[ky][c][1]);
+    }
+
     float res[VW][F][D];
     const T *mbase = mask + static_cast<int64_t>(b) * 9 * F * F * plane + static_cast<int64_t>(h) * W + w0;
 #pragma unroll
@@ -137,20 +164,33 @@ __global__ void __launch_bounds__(128) upsample_field_vec_kernel(const T *__rest
             float mx = lg[0][c];
 #pragma unroll
             for (int k = 1; k < 9; ++k) mx = fmaxf(mx, lg[k][c]);
+            // exp(l - mx) as 2^(l * log2e - mx * log2e), one fused multiply-add and one special-function op
+            constexpr float kLog2e = 1.4426950408889634f;
+            const float shift = -mx * kLog2e;
             float p[9], den = 0.f;
 #pragma unroll
             for (int k = 0; k < 9; ++k) {
-                p[k] = __expf(lg[k][c] - mx);
+                p[k] = exp2_approx(fmaf(lg[k][c], kLog2e, shift));
                 den += p[k];
             }
             const float inv = __frcp_rn(den);
 #pragma unroll
             for (int d = 0; d < D; ++d) res[c][j][d] = 0.f;
+            if constexpr (EPW == 2 && D == 2) {
+                // both components of a neighbour are one packed word: weight (rounded to T, broadcast)
+                // times word in one packed multiply, each rounded product added to its float32 sum
 #pragma unroll
-            for (int k = 0; k < 9; ++k) {
-                const float pk = DT<T>::rnd(p[k] * inv);
+                for (int k = 0; k < 9; ++k) {
+                    const float pf = p[k] * inv;
+                    DT<T>::wmul(word_as_pair<T>(DT<T>::aw_from(pf, pf)), nbw[k / 3][c + k % 3], &res[c][j][0]);
+                }
+            } else {
 #pragma unroll
-                for (int d = 0; d < D; ++d) res[c][j][d] += DT<T>::rnd(pk * nb[k / 3][c + k % 3][d]);
+                for (int k = 0; k < 9; ++k) {
+                    const float pk = DT<T>::rnd(p[k] * inv);
+#pragma unroll
+                    for (int d = 0; d < D; ++d) res[c][j][d] += DT<T>::rnd(pk * nb[k / 3][c + k % 3][d]);
+                }
             }
         }
     }
