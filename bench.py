@@ -143,8 +143,8 @@ def make_workload(name, seed):
     return dict(B=B, H=H, W=W, h=h, hd=hd, r=r, dtype=dtype, scale=hd ** -0.5, inputs=(mo, q, k, v))
 
 
-def time_cpu_port(wl, budget_s=12.0, nthreads=0):
-    """The oracle port on the host cores over one batch item of the workload, repeated."""
+def time_cpu_port(wl, budget_s=8.0, nthreads=0):
+    """The oracle port (C restatement) on the host cores over one batch item of the workload, repeated."""
     import oracle
     mo, q, k, v = (t[:1].contiguous() for t in wl["inputs"])
     H, W, r = wl["H"], wl["W"], wl["r"]
@@ -159,29 +159,71 @@ def time_cpu_port(wl, budget_s=12.0, nthreads=0):
     return H * W * reps / t_total, cores, reps, t_total
 
 
+def reference_cpu_step(wl):
+    """A callable running the reference's own PyTorch path (models/mat_pytorch_impl.py, driven as
+    models/attention_blocks.py:82-91 drives it) on the host cores over one batch item of the workload, in
+    float32 (PyTorch's CPU kernels for 16-bit types are not what anybody would time), with every host
+    thread PyTorch can use.  None when the reference's code is not present."""
+    from oracle import ref_loader
+    if not ref_loader.available():
+        return None, 0
+    impl, _ = ref_loader.import_reference()
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    mo, q, k, v = (t[:1].float().contiguous() for t in wl["inputs"])
+    H, W, h, r, scale = wl["H"], wl["W"], wl["h"], wl["r"], wl["scale"]
+
+    def step():
+        with torch.inference_mode():
+            return ref_loader.reference_op(impl, mo, q, k, v, H, W, h, r, scale)
+    return step, torch.get_num_threads()
+
+
+def time_cpu_reference(wl, budget_s=12.0):
+    step, cores = reference_cpu_step(wl)
+    if step is None:
+        return None
+    step()
+    reps, t_total = 0, 0.0
+    while reps < 2 or (t_total < budget_s and reps < 20):
+        t0 = time.perf_counter()
+        step()
+        t_total += time.perf_counter() - t0
+        reps += 1
+    return wl["H"] * wl["W"] * reps / t_total, cores, reps, t_total
+
+
 def run_reference_arm(args, rank):
+    """The reference's CPU implementation of the path on the host cores: its own PyTorch code when the
+    unmodified copy under oracle/_ref/ is present, else the C restatement (kind says which)."""
     if rank != 0:
         return
     wl = make_workload(args.workload, 1234)
-    import oracle
     H, W, r = wl["H"], wl["W"], wl["r"]
-    mo, q, k, v = (t[:1].contiguous() for t in wl["inputs"])
-    cores = oracle.max_threads()
-    for _ in range(max(1, min(args.warmup, 3))):
-        oracle.forward(mo, q, k, v, H, W, r, wl["scale"])
+    step, cores = reference_cpu_step(wl)
+    kind = "reference"
+    what = "models/mat_pytorch_impl.py of the reference (unmodified), float32, torch CPU threads = cores"
+    if step is None:
+        import oracle
+        mo, q, k, v = (t[:1].contiguous() for t in wl["inputs"])
+        cores, kind = oracle.max_threads(), "port"
+        what = f"C restatement of the reference algorithm, {DTYPE_NAME[wl['dtype']]} rounding points emulated"
+
+        def step():
+            return oracle.forward(mo, q, k, v, H, W, r, wl["scale"])
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
     steps = max(1, min(args.steps, 20))
     t0 = time.perf_counter()
     for _ in range(steps):
-        oracle.forward(mo, q, k, v, H, W, r, wl["scale"])
+        step()
     dt = time.perf_counter() - t0
     value = H * W * steps / dt
-    sample = f"one batch item ({H * W} queries) of the workload per step, {steps} steps, {DTYPE_NAME[wl['dtype']]} " \
-             f"arithmetic emulated with the reference's rounding points"
+    sample = f"one batch item ({H * W} queries) of the workload per step, {steps} steps; {what}"
     line = {"impl": "reference", "metric": "matchattention_queries_per_s", "value": value, "unit": "queries/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_NAME[wl["dtype"]],
             "data": "synthetic", "config": config_dict(args.workload, wl),
-            "cpu_baseline": {"value": value, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "queries/s", "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -393,6 +435,147 @@ def run_model_ops_mode(args):
     print(json.dumps(line), flush=True)
 
 
+def run_model_mode(args):
+    """The reference's own MatchStereo forward on the GPU with its operator swapped (BASELINE.json configs[2]:
+    MatchStereo-T, random-init weights, float16, a 1536x1536 synthetic stereo pair; ms per pair).
+
+    The model is the unmodified reference code (the copy oracle/make_ref.py places under oracle/_ref/): it is
+    the harness around the operator, not the thing built here.  Arms, all on the same GPU, same weights, same
+    pair, each timed with the reference's protocol (models run_img.py:100-112: warm-up, then the mean of the
+    timed forwards between two CUDA events):
+      pytorch        mat_impl='pytorch' (the reference's five torch functions), eager
+      dropin         mat_impl='cuda' with this library behind the module name match_attention, eager
+      fused          dropin + the steps around the operator on this library's kernels (dropin/fused_model.py)
+      fused_graph    the fused forward captured once as a CUDA graph and replayed
+    plus the 52 operator calls of the forward, with the inputs the model really gave them, replayed alone as
+    one CUDA graph (the operator's share of the forward)."""
+    import types
+    from oracle import ref_loader
+    metric = f"matchstereo_{args.model_variant}_{args.model_size[0]}x{args.model_size[1]}_ms_per_pair"
+    if not ref_loader.available():
+        print(json.dumps({"metric": metric, "unavailable": "the reference's Python code is not present under "
+                          "oracle/_ref/ (oracle/make_ref.py places it where a checkout exists)"}), flush=True)
+        return
+    import matchattention_b200 as ma
+    from matchattention_b200.dropin.fused_model import patch_reference_model
+    from _cases import make_stereo_pair
+    ref_loader.import_reference()
+    from models.match_stereo import MatchStereo
+    from models.match_former_ops import MF_FusedForwardOps
+    ma.install_dropin()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.backends.cudnn.benchmark = True
+    dtype = {"f16": torch.float16, "f32": torch.float32, "bf16": torch.bfloat16}[args.model_dtype]
+    Hi, Wi = args.model_size
+    stereo = not args.model_flow
+    left, right = make_stereo_pair(11, Hi, Wi, args.model_max_disp)
+    left, right = left.to(dev, dtype), right.to(dev, dtype)
+
+    def build(mat_impl):
+        torch.manual_seed(21)
+        m = MatchStereo(types.SimpleNamespace(variant=args.model_variant, mat_impl=mat_impl))
+        return m.eval().to(dev).to(dtype)
+
+    n = max(5, min(args.steps, 50))
+    warm = max(5, args.warmup)
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1.0))
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    t_wall0 = time.perf_counter()
+    arms, parity, notes = {}, {}, {}
+    with torch.inference_mode():
+        ref_model = build("pytorch")
+        want = ref_model(left, right, stereo=stereo)
+        arms["pytorch"] = timed(lambda: ref_model(left, right, stereo=stereo))
+        del ref_model
+        torch.cuda.empty_cache()
+
+        model = build("cuda")
+        # the operator calls of one forward, with their real inputs
+        calls = []
+
+        def grab(mod, a, kw, out):
+            calls.append((a[0], a[1], a[2], a[3], a[4], a[5], a[6][0], kw["scale"]))
+        hooks = [m.register_forward_hook(grab, with_kwargs=True) for m in model.modules()
+                 if isinstance(m, MF_FusedForwardOps)]
+        got = model(left, right, stereo=stereo)
+        for hk in hooks:
+            hk.remove()
+        parity["dropin_field_up_rel"] = rel(got["field_up"], want["field_up"])
+        arms["dropin"] = timed(lambda: model(left, right, stereo=stereo))
+
+        outs = [(torch.empty_like(c[1]), c[1].new_empty(c[1].size(0), c[1].size(1), c[0].size(2), (2 * c[6] + 2) ** 2))
+                for c in calls]
+
+        def ops_only():
+            for (mo, q, k, v, H, W, r, scale), (o, a) in zip(calls, outs):
+                ma.launch(mo, q, k, v, o, a, H, W, (r, r), "l1_norm", scale)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            ops_only()
+            gops = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gops, stream=side):
+                ops_only()
+        torch.cuda.synchronize()
+        op_ms = timed(gops.replay)
+        n_calls = len(calls)
+        alg = sum(c[1].element_size() * (4 * c[1].numel() + c[0].numel() + o[1].numel()) for c, o in zip(calls, outs))
+        del calls, outs, gops
+
+        patch_reference_model(model)
+        got = model(left, right, stereo=stereo)
+        parity["fused_field_up_rel"] = rel(got["field_up"], want["field_up"])
+        arms["fused"] = timed(lambda: model(left, right, stereo=stereo))
+
+        try:
+            static = {}
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    model(left, right, stereo=stereo)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    static["out"] = model(left, right, stereo=stereo)
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            parity["fused_graph_field_up_rel"] = rel(static["out"]["field_up"], want["field_up"])
+            arms["fused_graph"] = timed(graph.replay)
+        except Exception as exc:          # a step of the model that cannot be captured
+            notes["fused_graph"] = "not captured: " + str(exc).splitlines()[0][:200]
+            torch.cuda.synchronize()
+    sampler.stop()
+    best = min((v, k) for k, v in arms.items() if k != "pytorch")
+    line = {"metric": metric, "value": best[0], "unit": "ms", "n_gpus": 1, "steps": n, "warmup": warm,
+            "ms_per_step": best[0], "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.model_dtype, "data": "synthetic",
+            "config": {"workload": f"MatchStereo-{args.model_variant} forward, {Hi}x{Wi} pair, "
+                                   f"{'stereo' if stereo else 'flow'}, random-init weights (seed 21), batch of 2 views",
+                       "arm_reported": best[1], "arms_ms_per_pair": arms, "notes": notes,
+                       "field_up_rel_diff_vs_pytorch_branch": parity,
+                       "operator_calls": n_calls, "operator_calls_alone_graph_ms": op_ms,
+                       "operator_algorithmic_bytes": alg, "operator_algorithmic_GBps": alg / op_ms / 1e6,
+                       "target_ms": 5.0},
+            "clocks": sampler.summary(t_wall0, time.perf_counter()),
+            "gpu_launches": n_calls * n}
+    print(json.dumps(line), flush=True)
+
+
 def run_upsample_mode(args):
     """The convex upsampling of the field that follows the last MatchAttention block of MatchStereo at
     1536x1536: field [2, 384, 384, 2] x 4, mask [2, 144, 384, 384], float16."""
@@ -473,13 +656,18 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--mode", choices=["pairs", "band", "model_ops", "upsample", "volume"], default="pairs",
+    ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
     ap.add_argument("--band-kv", choices=["broadcast", "halo"], default="broadcast",
                     help="band mode: replicate all of K/V (NCCL broadcast) or only the rows a band can reach")
     ap.add_argument("--band-resident", action="store_true",
                     help="band mode: q / max_offset / outputs stay distributed, only K/V move each step")
+    ap.add_argument("--model-variant", default="tiny", choices=["tiny", "small", "base"])
+    ap.add_argument("--model-size", type=int, nargs=2, default=[1536, 1536], metavar=("H", "W"))
+    ap.add_argument("--model-dtype", default="f16", choices=["f16", "bf16", "f32"])
+    ap.add_argument("--model-max-disp", type=int, default=192)
+    ap.add_argument("--model-flow", action="store_true", help="model mode: optical-flow forward (stereo=False)")
     ap.add_argument("--tile-w", type=int, default=0)
     ap.add_argument("--chunks-per-lane", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="time K plain launches instead of one graph of K launches")
@@ -504,6 +692,9 @@ def main():
         return
     if args.mode == "model_ops":
         run_model_ops_mode(args)
+        return
+    if args.mode == "model":
+        run_model_mode(args)
         return
     if args.mode == "upsample":
         run_upsample_mode(args)
@@ -652,10 +843,18 @@ def main():
             line["e2e"] = e2e
         if not args.no_cpu_baseline:
             cpu_qps, cores, reps, secs = time_cpu_port(wl)
-            line["cpu_baseline"] = {
-                "value": cpu_qps, "unit": "queries/s", "cores": cores, "kind": "port",
-                "sample": f"one batch item ({H * W} queries) of the workload, {reps} repetitions in {secs:.1f} s, "
-                          f"C restatement of the reference algorithm with its {DTYPE_NAME[dtype]} rounding points"}
+            port = {"value": cpu_qps, "unit": "queries/s", "cores": cores, "kind": "port",
+                    "sample": f"one batch item ({H * W} queries) of the workload, {reps} repetitions in {secs:.1f} s, "
+                              f"C restatement of the reference algorithm with its {DTYPE_NAME[dtype]} rounding points"}
+            ref = time_cpu_reference(wl)
+            if ref is not None:
+                line["cpu_baseline"] = {
+                    "value": ref[0], "unit": "queries/s", "cores": ref[1], "kind": "reference",
+                    "sample": f"one batch item ({H * W} queries) of the workload, {ref[2]} repetitions in {ref[3]:.1f} s, "
+                              "models/mat_pytorch_impl.py of the reference (unmodified) in float32 on the host cores"}
+                line["cpu_port"] = port
+            else:
+                line["cpu_baseline"] = port
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

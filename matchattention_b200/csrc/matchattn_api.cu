@@ -46,7 +46,8 @@ BinGeometry bin_geometry(int B, int H, int W, int h, int hd, int r, int dtype, i
     gmt.RW = TX + 2 * r + 1; gmt.RH = TY + 2 * r + 1;
     gmt.bins_x = (W + TX - 1) / TX; gmt.bins_y = (H + TY - 1) / TY;
     const long long nbins = 1LL * B * gmt.bins_x * gmt.bins_y, nq = 1LL * B * rows * W;
-    if (nbins >= (1LL << 30) || nq >= (1LL << 31)) return gmt;
+    // the kernels index (query, head) items of one bin, and of the whole call, with 32-bit integers
+    if (nbins >= (1LL << 30) || nq * h >= (1LL << 31)) return gmt;
     gmt.nbins = static_cast<int>(nbins);
     gmt.region_bytes = static_cast<int>(region(TX, TY));
     auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };

@@ -67,13 +67,11 @@ cudaError_t launch_mma<MATCHATTN_T>(const Params &p, int cpl, bool sameq, bool p
 template <typename T, int CPL, bool SAMEQ>
 static cudaError_t launch_binned_one(const BinParams &bp, int grid_blocks, size_t smem_bytes, cudaStream_t stream)
 {
-    static bool configured = false;      // per instantiation; a repeated set is harmless
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(binned_forward_kernel<T, CPL, SAMEQ>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxBinnedSmem));
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    // The opt-in to large dynamic shared memory is a per-device attribute of the kernel: it is set on
+    // every launch (cheap, idempotent, safe from any host thread) rather than remembered per process.
+    cudaError_t e = cudaFuncSetAttribute(binned_forward_kernel<T, CPL, SAMEQ>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxBinnedSmem));
+    if (e != cudaSuccess) return e;
     binned_forward_kernel<T, CPL, SAMEQ><<<grid_blocks, kBinThreads, smem_bytes, stream>>>(bp);
     return cudaGetLastError();
 }

@@ -58,6 +58,8 @@ extern "C" int matchattn_fused_forward_static(const void *max_offset, const void
                                               int q_row_end, void *cuda_stream)
 {
     if (rx != ry) return MATCHATTN_ERR_WINDOW;
+    if (B <= 0 || H <= 0 || W <= 0 || h <= 0 || hd <= 0 || q_row_begin < 0 || q_row_end > H || q_row_begin >= q_row_end)
+        return MATCHATTN_ERR_SHAPE;
     // sizes first: nothing is launched and no address is looked up for a problem that does not fit
     const size_t need = matchattn_workspace_bytes(B, H, W, h, hd, rx, dtype, q_row_begin, q_row_end);
     if (need == 0) return MATCHATTN_ERR_VARIANT;             // the binned path does not cover these arguments

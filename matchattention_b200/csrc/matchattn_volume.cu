@@ -72,13 +72,10 @@ __global__ void __launch_bounds__(256) stereo_volume_kernel(const T *__restrict_
 template <typename T>
 cudaError_t launch(const void *corr, void *vol, int B, int H, int W, size_t smem, cudaStream_t stream)
 {
-    static bool configured = false;      // per instantiation; a repeated set is harmless
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(stereo_volume_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             200 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    // per-device attribute of the kernel: set on every launch (cheap, idempotent, thread-safe)
+    cudaError_t e = cudaFuncSetAttribute(stereo_volume_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         200 * 1024);
+    if (e != cudaSuccess) return e;
     stereo_volume_kernel<T><<<dim3(H, 2 * B), 256, smem, stream>>>(static_cast<const T *>(corr), static_cast<T *>(vol), B, H, W);
     return cudaGetLastError();
 }

@@ -100,9 +100,10 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
     ``strategy``: 0 lets the library choose (currently the direct kernel), 1 forces
     the direct kernel, 2 the binned path (queries sorted by target tile, K/V tiles
     staged in shared memory; 16-bit types, r = 1, head width <= 40).  The binned path needs scratch
-    memory: ``workspace`` (a uint8 CUDA tensor) or, by default, a buffer this module
-    keeps per device and stream.  The tuning knobs (tile_w, force_generic,
-    chunks_per_lane, variant) belong to the direct kernels and imply strategy 1.
+    memory: ``workspace`` (a uint8 CUDA tensor) or, when strategy >= 2 is asked for without one, a
+    buffer this module allocates once per (device, stream) and keeps; strategy 0 and 1 allocate
+    nothing.  The tuning knobs (tile_w, force_generic, chunks_per_lane, variant) belong to the
+    direct kernels and imply strategy 1.
     """
     rx, ry = _window_radius(win_r)
     if q_row_end is None:
@@ -123,6 +124,9 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
         if knobs or strategy == STRATEGY_DIRECT:
             status = _lib.lib.matchattn_fused_forward_ex(*args, int(tile_w), int(bool(force_generic)),
                                                          int(chunks_per_lane), int(variant))
+        elif strategy == STRATEGY_AUTO and workspace is None:
+            # the library's own choice needs no scratch: nothing is looked up or allocated here
+            status = _lib.lib.matchattn_fused_forward(*args)
         else:
             need = workspace_bytes(B, H, W, h, hd, rx, q.dtype, q_row_begin, q_row_end) if rx == ry else 0
             ws_ptr, ws_len = None, 0
@@ -268,6 +272,9 @@ def upsample_field(field: torch.Tensor, mask: torch.Tensor, factor: int) -> torc
                                                    torch.cuda.current_stream().cuda_stream)
     _lib.check(status)
     return out
+
+
+STEREO_VOLUME_MAX_W = 159      # the row's W x W slice must fit the kernel's shared memory
 
 
 def stereo_volume(correlation: torch.Tensor) -> torch.Tensor:

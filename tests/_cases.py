@@ -189,3 +189,36 @@ def make_inputs(seed, B, H, W, h, hd, r, dtype, kind="flow", spread=24.0, border
     else:
         raise ValueError(kind)
     return mo, q, k, v
+
+
+def make_stereo_pair(seed, H, W, max_disp, device="cpu", planes=(3, 4)):
+    """Seeded synthetic stereo pair with the statistics BASELINE.json's model configs name: the left image
+    is uniform RGB noise blurred with a Gaussian of sigma 2, the right image is the left one warped by a
+    piecewise-planar disparity field in [0, max_disp] px, plus N(0, 0.02) noise (on the 0..1 scale).
+    Returns (left, right) as float32 [1, 3, H, W] in 0..255, as the reference's loader delivers them."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(seed)
+    left = torch.rand(1, 3, H, W, generator=g)
+    radius = 6
+    xs = torch.arange(-radius, radius + 1, dtype=torch.float32)
+    kern = torch.exp(-xs * xs / (2 * 2.0 ** 2))
+    kern = (kern / kern.sum()).view(1, 1, 1, -1).repeat(3, 1, 1, 1)
+    left = F.conv2d(F.pad(left, (radius, radius, 0, 0), mode="reflect"), kern, groups=3)
+    left = F.conv2d(F.pad(left, (0, 0, radius, radius), mode="reflect"), kern.transpose(2, 3), groups=3)
+    left = (left - left.amin()) / (left.amax() - left.amin())        # blur shrinks the range: stretch it back
+    # piecewise-planar disparity: a grid of patches, each its own plane d = a*x + b*y + c
+    py, px = planes
+    a = torch.empty(py, px).uniform_(-0.05, 0.05, generator=g)
+    b = torch.empty(py, px).uniform_(-0.05, 0.05, generator=g)
+    c = torch.empty(py, px).uniform_(0.1, 0.9, generator=g) * max_disp
+    yy, xx = torch.meshgrid(torch.arange(H, dtype=torch.float32), torch.arange(W, dtype=torch.float32), indexing="ij")
+    iy = (yy * py / H).long().clamp_(max=py - 1)
+    ix = (xx * px / W).long().clamp_(max=px - 1)
+    disp = (a[iy, ix] * (xx - W / 2) + b[iy, ix] * (yy - H / 2) + c[iy, ix]).clamp_(0.0, float(max_disp))
+    # the right view sees the point of left column x + d at column x
+    gx = 2 * (xx + disp) / (W - 1) - 1
+    gy = 2 * yy / (H - 1) - 1
+    right = F.grid_sample(left, torch.stack((gx, gy), -1)[None], mode="bilinear", padding_mode="border",
+                          align_corners=True)
+    right = (right + torch.randn(1, 3, H, W, generator=g) * 0.02).clamp_(0, 1)
+    return (left * 255).to(device), (right * 255).to(device)

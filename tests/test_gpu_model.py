@@ -1,0 +1,115 @@
+"""The reference's own MatchStereo model on the GPU, its operator swapped for this library.
+
+The unmodified reference code (the copy oracle/make_ref.py places under oracle/_ref/) is built twice
+with the same seeded random weights: once with ``mat_impl='pytorch'`` (models/attention_blocks.py:81-91,
+the five functions of models/mat_pytorch_impl.py) and once with ``mat_impl='cuda'`` after
+``matchattention_b200.install_dropin()``, so that models/match_former_ops.py:29-33 imports this library
+under the name ``match_attention``.  Checked:
+
+* every one of the 52 operator calls of the forward, through a forward hook on the reference's
+  MF_FusedForwardOps module: what the library wrote against the reference's functions run on the same
+  call's inputs on the same GPU, at the operator tolerance;
+* ``field_up`` and ``self_rpos`` of the two models against each other.  The error of 52 chained calls
+  and the layers between them compounds, so this gate is looser (stated below) and the per-call gate
+  above is the strict one;
+* the same model with the steps around the operator fused as well (dropin/fused_model.py).
+"""
+import os
+import sys
+import types
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from _cases import assert_close, excess, make_stereo_pair  # noqa: E402
+from oracle import ref_loader  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+if not ref_loader.available():
+    pytest.skip("the reference's Python code is not present (oracle/make_ref.py places it under oracle/_ref/)",
+                allow_module_level=True)
+
+# End-to-end gate on field_up / self_rpos, relative to the largest magnitude of the reference output.
+# float32: the per-call differences are a few float32 ulps and the network amplifies them.
+# float16: a last-bit difference in one attention weight moves the field by a 16-bit ulp and every
+# later layer samples at the moved position.
+E2E_REL_TOL = {torch.float32: 2e-3, torch.float16: 6e-2}
+
+
+def build_model(mat_impl, dtype, seed=21, variant="tiny"):
+    ref_loader.import_reference()
+    from models.match_stereo import MatchStereo
+    torch.manual_seed(seed)
+    model = MatchStereo(types.SimpleNamespace(variant=variant, mat_impl=mat_impl))
+    return model.eval().cuda().to(dtype)
+
+
+def images(dtype, H=384, W=512, max_disp=48):
+    left, right = make_stereo_pair(5, H, W, max_disp)
+    return left.cuda().to(dtype), right.cuda().to(dtype)
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1.0))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("stereo", [True, False], ids=["stereo", "flow"])
+def test_reference_model_with_operator_swapped(dtype, stereo):
+    import matchattention_b200 as ma
+    impl, _ = ref_loader.import_reference()
+    ma.install_dropin()
+    left, right = images(dtype)
+    with torch.inference_mode():
+        want = build_model("pytorch", dtype)(left, right, stereo=stereo)
+
+        model = build_model("cuda", dtype)
+        calls = []
+
+        def check_call(mod, args, kwargs, output):
+            mo, q, k, v, H, W, win_r, attn_num = args[:8]
+            h, r = mo.size(2), win_r[0]
+            ref_out, ref_attn = ref_loader.reference_op(impl, mo, q, k, v, H, W, h, r, kwargs["scale"])
+            out, attn = output
+            wide = q.size(-1) // h > 16          # score sums of wide heads are not exact in float32 (rounding ties)
+            calls.append((H, W, r, q.size(-1) // h, excess(out, ref_out, dtype), excess(attn, ref_attn, dtype)))
+            assert_close(attn, ref_attn, dtype, f"call {len(calls)} ({H}x{W}, r={r}) attn", ties=wide)
+            assert_close(out, ref_out, dtype, f"call {len(calls)} ({H}x{W}, r={r}) out", ties=wide)
+
+        from models.match_former_ops import MF_FusedForwardOps
+        hooks = [m.register_forward_hook(check_call, with_kwargs=True) for m in model.modules()
+                 if isinstance(m, MF_FusedForwardOps)]
+        got = model(left, right, stereo=stereo)
+        for hk in hooks:
+            hk.remove()
+    torch.cuda.synchronize()
+    assert len(calls) == 52, f"expected 52 operator calls per forward, saw {len(calls)}"
+    for key in ("field_up", "self_rpos"):
+        e = rel_err(got[key], want[key])
+        print(f"{key}: relative difference {e:.3e} ({dtype}, stereo={stereo})")
+        assert e <= E2E_REL_TOL[dtype], f"{key} differs from the 'pytorch' branch by {e:.3e} (relative)"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+def test_reference_model_with_fused_steps(dtype):
+    """Operator + clamp/gate/concat, convex upsampling, cost volume and consistency mask on this
+    library's kernels, against the reference's 'pytorch' branch."""
+    import matchattention_b200 as ma
+    from matchattention_b200.dropin.fused_model import patch_reference_model, unpatch_reference_model
+    ma.install_dropin()
+    left, right = images(dtype)
+    with torch.inference_mode():
+        want = build_model("pytorch", dtype)(left, right, stereo=True)
+        model = patch_reference_model(build_model("cuda", dtype))
+        got = model(left, right, stereo=True)
+        unpatch_reference_model(model)
+        again = model(left, right, stereo=True)
+    torch.cuda.synchronize()
+    for key in ("field_up", "self_rpos", "init_flow"):
+        e = rel_err(got[key], want[key])
+        print(f"fused {key}: relative difference {e:.3e} ({dtype})")
+        assert e <= E2E_REL_TOL[dtype], f"fused {key} differs from the 'pytorch' branch by {e:.3e} (relative)"
+        assert rel_err(again[key], want[key]) <= E2E_REL_TOL[dtype]
