@@ -30,7 +30,29 @@ def ulp16(ref, dtype):
 def golden_names(pattern="*"):
     """Golden files of the operator (the upsample_* files belong to load_golden_upsample)."""
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, pattern + ".npz")))
-    return [n for n in names if not n.startswith(("upsample_", "volume_"))]
+    return [n for n in names if not n.startswith(("upsample_", "volume_", "sampled_", "consistency_", "disparity_",
+                                                  "flowinit_"))]
+
+
+def golden_sampled_names():
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "sampled_*.npz")))
+
+
+def load_golden_sampled(name):
+    """A full-size case stored as generator parameters + the reference's outputs at a subset of the
+    queries.  Returns the regenerated inputs, the query index and the expected rows."""
+    import hashlib
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    dt = DTYPES[str(z["dtype"])]
+    B, H, W, h, hd, r = (int(z[n]) for n in ("B", "H", "W", "h", "hd", "r"))
+    kind = str(z["kind"])
+    inputs = make_inputs(int(z["seed"]), B, H, W, h, hd, r, dt, kind=kind, spread=float(z["spread"]), border_frac=0.0,
+                         per_head=(kind == "self"))
+    digest = hashlib.sha256(b"".join(t.numpy().tobytes() for t in inputs)).hexdigest()
+    assert digest == str(z["inputs_sha256"]), "make_inputs no longer reproduces the inputs this file was made from"
+    return dict(dtype=dt, B=B, H=H, W=W, h=h, hd=hd, r=r, scale=float(z["scale"]), inputs=inputs,
+                index=torch.from_numpy(z["query_index"].copy()), out=torch.from_numpy(z["out"].copy()),
+                attn=torch.from_numpy(z["attn"].copy()))
 
 
 def golden_upsample_names():

@@ -26,57 +26,8 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def install_timm_shim():
-    """The reference imports four helpers from timm, which is not installed."""
-    if "timm" in sys.modules:
-        return
-    import torch.nn as nn
-
-    class DropPath(nn.Module):
-        def __init__(self, p=0.0):
-            super().__init__()
-
-        def forward(self, x):
-            return x
-
-    def to_2tuple(x):
-        return tuple(x) if isinstance(x, (tuple, list)) else (x, x)
-
-    def register_model(fn):
-        return fn
-
-    pkgs = {n: types.ModuleType(n) for n in (
-        "timm", "timm.models", "timm.models.layers", "timm.models.layers.helpers", "timm.models.registry")}
-    pkgs["timm.models.layers"].DropPath = DropPath
-    pkgs["timm.models.layers"].trunc_normal_ = torch.nn.init.trunc_normal_
-    pkgs["timm.models.layers.helpers"].to_2tuple = to_2tuple
-    pkgs["timm.models.registry"].register_model = register_model
-    pkgs["timm"].models = pkgs["timm.models"]
-    pkgs["timm.models"].layers = pkgs["timm.models.layers"]
-    pkgs["timm.models"].registry = pkgs["timm.models.registry"]
-    pkgs["timm.models.layers"].helpers = pkgs["timm.models.layers.helpers"]
-    sys.modules.update(pkgs)
-
-
-def import_reference(ref_root):
-    install_timm_shim()
-    sys.path.insert(0, ref_root)
-    import models.mat_pytorch_impl as impl
-    import models.attention_blocks as blocks
-    return impl, blocks
-
-
-def reference_op(impl, max_offset, q, k, v, H, W, h, r, scale):
-    """The 'pytorch' branch of MatchAttention.forward (attention_blocks.py:82-91), no dropout."""
-    B, N, _ = q.shape
-    win_r = [r, r]
-    m_id = torch.floor(max_offset).to(torch.int32)
-    wgt = impl.compute_bilinear_weights(max_offset)
-    attn, idx = impl.compute_match_attention(q.view(B, N, h, -1), k.view(B, N, h, -1), m_id, win_r, H, W)
-    attn = attn * scale
-    attn = impl.compute_bilinear_softmax(attn, wgt, win_r)
-    out = impl.attention_aggregate(v.view(B, N, h, -1), attn, idx, win_r)
-    return out, attn
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle.ref_loader import import_reference, install_timm_shim, reference_op  # noqa: E402,F401
 
 
 def reference_clamp(blocks, max_offset, H, W, r):
@@ -140,6 +91,56 @@ def synthetic_cases(impl, blocks):
             tag = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[dtype]
             save_case(f"{name}_{tag}", dtype, H, W, h, r, scale, mo, q, k, v, out, attn,
                       f"seed {seed}, kind {kind}, reference mat_pytorch_impl on CPU")
+
+
+def wide_head_cases(impl, blocks):
+    """Head widths of the small and base model variants (64, 80, 128) and beyond, where the float32 sum
+    of a score is no longer exact: small maps, float32 / float16 / bfloat16."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    from _cases import make_inputs
+    specs = [
+        # name, seed, B, H, W, h, hd, r, kind
+        ("wide_hd64_r1", 51, 1, 11, 13, 4, 64, 1, "flow"),
+        ("wide_hd80_r2", 52, 1, 9, 10, 4, 80, 2, "raw"),
+        ("wide_hd128_r1", 53, 1, 8, 9, 2, 128, 1, "raw"),
+        ("wide_hd256_r1", 54, 1, 6, 7, 2, 256, 1, "flow"),
+    ]
+    for name, seed, B, H, W, h, hd, r, kind in specs:
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            mo, q, k, v = make_inputs(seed, B, H, W, h, hd, r, dtype, kind=kind, spread=W / 3, per_head=True,
+                                      border_frac=0.2)
+            scale = hd ** -0.5
+            out, attn = reference_op(impl, mo, q, k, v, H, W, h, r, scale)
+            tag = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[dtype]
+            save_case(f"{name}_{tag}", dtype, H, W, h, r, scale, mo, q, k, v, out, attn,
+                      f"_cases.make_inputs(seed {seed}, kind {kind}, spread W/3, per_head, border_frac 0.2), "
+                      "reference mat_pytorch_impl on CPU")
+
+
+def sampled_full_size_cases(impl):
+    """The CPU-runnable configuration at full size (B=1, 104x208 tokens, 8 heads x 16, r=1; cross and self
+    offsets; float32 and float16).  Inputs are regenerated from the seed by tests/_cases.make_inputs (a
+    SHA-256 of their bytes is stored to catch a generator that changed); of the reference's outputs every
+    26th query is stored, which keeps a file below a megabyte."""
+    import hashlib
+    sys.path.insert(0, os.path.dirname(HERE))
+    from _cases import make_inputs
+    B, H, W, h, hd, r, stride = 1, 104, 208, 8, 16, 1, 26
+    for kind, seed, spread in (("cross", 61, 16.0), ("self", 62, 3.0)):
+        for dtype in (torch.float32, torch.float16):
+            mo, q, k, v = make_inputs(seed, B, H, W, h, hd, r, dtype, kind=kind, spread=spread, border_frac=0.0,
+                                      per_head=(kind == "self"))
+            out, attn = reference_op(impl, mo, q, k, v, H, W, h, r, hd ** -0.5)
+            digest = hashlib.sha256(b"".join(to_np(t).tobytes() for t in (mo, q, k, v))).hexdigest()
+            idx = torch.arange(0, H * W, stride)
+            tag = {torch.float32: "f32", torch.float16: "f16"}[dtype]
+            path = os.path.join(HERE, f"sampled_config0_{kind}_{tag}.npz")
+            np.savez_compressed(path, dtype=str(dtype).replace("torch.", ""), B=B, H=H, W=W, h=h, hd=hd, r=r,
+                                seed=seed, kind=kind, spread=spread, scale=np.float64(hd ** -0.5),
+                                inputs_sha256=digest, query_index=idx.numpy(), out=to_np(out[:, idx]),
+                                attn=to_np(attn[:, idx]),
+                                note="reference mat_pytorch_impl on CPU at full size; every 26th query stored")
+            print(f"sampled_config0_{kind}_{tag}: {os.path.getsize(path) / 1024:.0f} KiB")
 
 
 def model_cases(ref_root, impl):
@@ -246,11 +247,18 @@ def main():
                     help="checkout of the reference project (or set MATCHATTN_REF)")
     ap.add_argument("--skip-model", action="store_true")
     ap.add_argument("--only-upsample", action="store_true", help="regenerate only the upsample_field vectors")
+    ap.add_argument("--only-new", action="store_true", help="only the wide-head and sampled full-size operator vectors")
     a = ap.parse_args()
     impl, blocks = import_reference(a.ref)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if a.only_new:
+        wide_head_cases(impl, blocks)
+        sampled_full_size_cases(impl)
+        return
     if not a.only_upsample:   # (the flag also regenerates the cost-volume vectors)
         synthetic_cases(impl, blocks)
+        wide_head_cases(impl, blocks)
+        sampled_full_size_cases(impl)
         if not a.skip_model:
             model_cases(a.ref, impl)
     upsample_cases(a.ref)

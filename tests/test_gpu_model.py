@@ -35,7 +35,8 @@ if not ref_loader.available():
 # float32: the per-call differences are a few float32 ulps and the network amplifies them.
 # float16: a last-bit difference in one attention weight moves the field by a 16-bit ulp and every
 # later layer samples at the moved position.
-E2E_REL_TOL = {torch.float32: 2e-3, torch.float16: 6e-2}
+# Observed on a B200 (MatchStereo-tiny, 384x512 pair): float32 5e-7 .. 9e-5, float16 1.8e-3 .. 3.8e-3.
+E2E_REL_TOL = {torch.float32: 1e-3, torch.float16: 2e-2}
 
 
 def build_model(mat_impl, dtype, seed=21, variant="tiny"):

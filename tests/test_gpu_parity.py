@@ -5,7 +5,8 @@ seeded inputs.  Tolerances: float32 1e-4 relative, float16 2e-3 absolute
 import pytest
 import torch
 
-from _cases import assert_close, excess, golden_names, load_golden, make_inputs
+from _cases import (assert_close, excess, golden_names, golden_sampled_names, load_golden, load_golden_sampled,
+                    make_inputs)
 
 pytestmark = pytest.mark.gpu
 
@@ -35,6 +36,16 @@ def test_kernel_matches_reference_vectors(name, force_generic):
                            force_generic=force_generic)
     assert_close(attn, c["attn"], c["dtype"], name + " attn")
     assert_close(out, c["out"], c["dtype"], name + " out")
+
+
+@pytest.mark.parametrize("name", golden_sampled_names())
+def test_kernel_matches_reference_at_full_size(name):
+    """The CPU-runnable configuration (104x208 tokens) at full size against the reference's own outputs
+    at every 26th query."""
+    c = load_golden_sampled(name)
+    out, attn = run_kernel(c["inputs"], c["H"], c["W"], c["r"], c["scale"])
+    assert_close(attn[:, c["index"]], c["attn"], c["dtype"], name + " attn")
+    assert_close(out[:, c["index"]], c["out"], c["dtype"], name + " out")
 
 
 SHAPES = [

@@ -6,7 +6,8 @@ import torch
 
 import oracle
 from oracle import matchattn_numpy
-from _cases import assert_close, excess, golden_names, load_golden, make_inputs
+from _cases import (assert_close, excess, golden_names, golden_sampled_names, load_golden, load_golden_sampled,
+                    make_inputs)
 
 
 @pytest.mark.parametrize("name", golden_names())
@@ -15,6 +16,16 @@ def test_c_oracle_matches_reference_vectors(name):
     out, attn = oracle.forward(c["max_offset"], c["q"], c["k"], c["v"], c["H"], c["W"], c["r"], c["scale"])
     assert_close(attn, c["attn"], c["dtype"], name + " attn")
     assert_close(out, c["out"], c["dtype"], name + " out")
+
+
+@pytest.mark.parametrize("name", golden_sampled_names())
+def test_c_oracle_matches_reference_at_full_size(name):
+    """The CPU-runnable configuration (104x208 tokens) at full size against the reference's outputs at
+    every 26th query."""
+    c = load_golden_sampled(name)
+    out, attn = oracle.forward(*c["inputs"], c["H"], c["W"], c["r"], c["scale"])
+    assert_close(attn[:, c["index"]], c["attn"], c["dtype"], name + " attn")
+    assert_close(out[:, c["index"]], c["out"], c["dtype"], name + " out")
 
 
 @pytest.mark.parametrize("name", golden_names("*_f16") + golden_names("*_bf16"))
