@@ -45,6 +45,7 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "op_384x384_b4_h8x16_r1_f16_flow"
 DTYPE_NAME = {torch.float16: "f16", torch.float32: "f32", torch.bfloat16: "bf16"}
 FALLBACK_HBM_GBS = 6650.0
+MIN_REGION_S = 0.3
 
 
 def algorithmic_bytes_per_query(h, hd, r, esize, with_attn=True):
@@ -62,17 +63,16 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, MEASURED_PEAKS.json absent)"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries
-# (profiles/fused_forward_f16_cpl2_op_384x384_b1.md: 168.9 MB for the one-item case; traffic is
-# proportional to the items of a launch, so the four-item bench launch moves four times that)
-NCU_TRAFFIC_BYTES = {
-    "op_384x384_b1_h8x16_r1_f16_flow": 168.9e6,
-    "op_384x384_b4_h8x16_r1_f16_flow": 4 * 168.9e6,
-}
-
-
 def ncu_traffic_per_launch(workload):
-    return NCU_TRAFFIC_BYTES.get(workload)
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from the table kept
+    beside the ncu summaries (profiles/ncu_traffic.json names the capture each figure comes from); None for
+    a workload that was never captured."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            entry = json.load(f).get(workload)
+        return float(entry["dram_bytes_per_launch"]) if entry else None
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -133,6 +133,30 @@ class ClockSampler:
         reasons = [name for bit, name in self.REASONS.items() if mask & bit]
         return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz, "reasons": reasons,
                 "samples": len(inside), "window": window}
+
+
+def bind_to_gpu_cpus(index):
+    """Restrict this process to the CPUs NVML reports as local to GPU `index` (a read-only query), so that
+    its threads and the pinned buffers they first touch sit on the GPU's NUMA node.  Returns a short
+    description for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = torch.cuda.get_device_properties(index).uuid
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (ncpu + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return "NVML's CPU set for the GPU does not intersect this process's: left unbound"
+        os.sched_setaffinity(0, allowed)
+        return f"bound to {len(allowed)} CPUs local to the GPU ({min(allowed)}-{max(allowed)})"
+    except Exception as exc:
+        return f"left unbound ({type(exc).__name__})"
 
 
 def make_workload(name, seed):
@@ -447,6 +471,8 @@ def run_model_mode(args):
       dropin         mat_impl='cuda' with this library behind the module name match_attention, eager
       fused          dropin + the steps around the operator on this library's kernels (dropin/fused_model.py)
       fused_graph    the fused forward captured once as a CUDA graph and replayed
+      fused_compiled / fused_compiled_graph / pytorch_compiled   (--model-compile) the same under torch.compile,
+                     which is how the reference's own driver runs the model
     plus the 52 operator calls of the forward, with the inputs the model really gave them, replayed alone as
     one CUDA graph (the operator's share of the forward)."""
     import types
@@ -543,8 +569,8 @@ def run_model_mode(args):
         parity["fused_field_up_rel"] = rel(got["field_up"], want["field_up"])
         arms["fused"] = timed(lambda: model(left, right, stereo=stereo))
 
+        static = {}
         try:
-            static = {}
             with torch.cuda.stream(side):
                 for _ in range(3):
                     model(left, right, stereo=stereo)
@@ -559,8 +585,48 @@ def run_model_mode(args):
         except Exception as exc:          # a step of the model that cannot be captured
             notes["fused_graph"] = "not captured: " + str(exc).splitlines()[0][:200]
             torch.cuda.synchronize()
+        if args.model_compile:
+            # torch.compile around the opaque ops, as the reference's own driver compiles its model
+            # (run_img.py:55-58: default mode, dynamic=False, TF32 matmuls allowed)
+            torch.backends.cuda.matmul.allow_tf32 = True
+            try:
+                patch_reference_model(model, traceable=True)
+                cmodel = torch.compile(model, dynamic=False)
+                t0 = time.perf_counter()
+                got = cmodel(left, right, stereo=stereo)
+                torch.cuda.synchronize()
+                notes["fused_compiled_compile_s"] = round(time.perf_counter() - t0, 1)
+                parity["fused_compiled_field_up_rel"] = rel(got["field_up"], want["field_up"])
+                arms["fused_compiled"] = timed(lambda: cmodel(left, right, stereo=stereo))
+                try:
+                    with torch.cuda.stream(side):
+                        for _ in range(3):
+                            cmodel(left, right, stereo=stereo)
+                        cgraph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(cgraph, stream=side):
+                            static["cout"] = cmodel(left, right, stereo=stereo)
+                    torch.cuda.synchronize()
+                    arms["fused_compiled_graph"] = timed(cgraph.replay)
+                    parity["fused_compiled_graph_field_up_rel"] = rel(static["cout"]["field_up"], want["field_up"])
+                except Exception as exc:
+                    notes["fused_compiled_graph"] = "not captured: " + str(exc).splitlines()[0][:200]
+                    torch.cuda.synchronize()
+            except Exception as exc:
+                notes["fused_compiled"] = "failed: " + str(exc).splitlines()[0][:300]
+            try:
+                del model
+                torch.cuda.empty_cache()
+                ref_model = build("pytorch")
+                cref = torch.compile(ref_model, dynamic=False)
+                t0 = time.perf_counter()
+                cref(left, right, stereo=stereo)
+                torch.cuda.synchronize()
+                notes["pytorch_compiled_compile_s"] = round(time.perf_counter() - t0, 1)
+                arms["pytorch_compiled"] = timed(lambda: cref(left, right, stereo=stereo))
+            except Exception as exc:
+                notes["pytorch_compiled"] = "failed: " + str(exc).splitlines()[0][:300]
     sampler.stop()
-    best = min((v, k) for k, v in arms.items() if k != "pytorch")
+    best = min((v, k) for k, v in arms.items() if not k.startswith("pytorch"))
     line = {"metric": metric, "value": best[0], "unit": "ms", "n_gpus": 1, "steps": n, "warmup": warm,
             "ms_per_step": best[0], "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
             "dtype": args.model_dtype, "data": "synthetic",
@@ -637,6 +703,51 @@ def run_volume_mode(args):
                       "higher_is_better": False, "dtype": "f16", "data": "synthetic", "config": {"shapes": rows}}), flush=True)
 
 
+SHAPE_WORKLOADS = ("op_384x384_b4_h8x16_r1_f32_flow", "op_384x384_b4_h8x16_r1_bf16_flow",
+                   "op_384x384_b4_h8x16_r1_f16_flow_perhead", "op_384x384_b4_h8x16_r1_f16_smooth",
+                   "op_104x208_b1_h8x16_r1_f32_cross", "op_96x96_b2_h4x32_r2_f16_self", "op_48x48_b2_h4x40_r2_f16_self")
+
+
+def time_shape(name, dev, peak, seed=4321, region_s=0.1):
+    """One other configuration shape, timed on the device the same way as the headline (a CUDA graph of the
+    launches, replayed until the region lasts `region_s`); returns the entry for the line's `shapes` list."""
+    import matchattention_b200 as ma
+    wl = make_workload(name, seed)
+    B, H, W, h, hd, r, dtype = (wl[n] for n in ("B", "H", "W", "h", "hd", "r", "dtype"))
+    mo, q, k, v = (t.to(dev) for t in wl["inputs"])
+    out, attn = torch.empty_like(q), q.new_empty(B, H * W, h, (2 * r + 2) ** 2)
+    per_graph = 20
+
+    def launches():
+        for _ in range(per_graph):
+            ma.launch(mo, q, k, v, out, attn, H, W, (r, r), "l1_norm", wl["scale"])
+    graph, cap = torch.cuda.CUDAGraph(), torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(cap):
+        launches()
+        with torch.cuda.graph(graph, stream=cap):
+            launches()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    reps = max(3, min(5000, int(region_s * 1e3 / max(e0.elapsed_time(e1), 1e-3)) + 1))
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / (reps * per_graph)
+    esize = 2 if dtype != torch.float32 else 4
+    nbytes = algorithmic_bytes_per_query(h, hd, r, esize) * B * H * W
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    return {"workload": name, "ms": ms, "queries_per_s": B * H * W / (ms * 1e-3), "achieved_GBps": achieved,
+            "frac": achieved / peak, "dispatch": ma.describe_dispatch(h, hd, r, dtype),
+            "algorithmic_MB": nbytes / 1e6, "launches_timed": reps * per_graph,
+            "l2": "exceeds L2" if nbytes > 126e6 else "fits L2 (resident between launches, as between the layers of the model)"}
+
+
 def config_dict(name, wl):
     step_mb = wl["B"] * wl["H"] * wl["W"] * algorithmic_bytes_per_query(wl["h"], wl["hd"], wl["r"],
                                                                         torch.empty(0, dtype=wl["dtype"]).element_size()) / 1e6
@@ -656,6 +767,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the timing of the other configuration shapes")
     ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
@@ -668,6 +780,8 @@ def main():
     ap.add_argument("--model-dtype", default="f16", choices=["f16", "bf16", "f32"])
     ap.add_argument("--model-max-disp", type=int, default=192)
     ap.add_argument("--model-flow", action="store_true", help="model mode: optical-flow forward (stereo=False)")
+    ap.add_argument("--model-compile", action="store_true",
+                    help="model mode: also time the model under torch.compile (minutes of compilation)")
     ap.add_argument("--tile-w", type=int, default=0)
     ap.add_argument("--chunks-per-lane", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="time K plain launches instead of one graph of K launches")
@@ -709,6 +823,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
+    binding = bind_to_gpu_cpus(local_rank)      # before any pinned allocation: first touch decides the NUMA node
     wl = make_workload(args.workload, 1234 + rank)
     B, H, W, h, hd, r, dtype = (wl[n] for n in ("B", "H", "W", "h", "hd", "r", "dtype"))
     M = (2 * r + 2) ** 2
@@ -748,14 +863,31 @@ def main():
                     step()
         run_steps = graph.replay
         barrier()
+    # The K-step region is repeated until it lasts MIN_REGION_S on the device (the kernel takes a fraction of
+    # a millisecond, K of them are too short a sample for the clock record); the per-step time is the mean.
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def k_steps():
+        if run_steps is not None:
+            run_steps()
+        else:
+            for _ in range(args.steps):
+                step()
+
+    ev0.record()
+    k_steps()
+    ev1.record()
+    barrier()
+    once_ms = max(ev0.elapsed_time(ev1), 1e-3)
+    reps = max(1, min(2000, int(MIN_REGION_S * 1e3 / once_ms) + 1))
+    if dist is not None:
+        t = torch.tensor([reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        reps = int(t.item())
     t_wall0 = time.perf_counter()
     ev0.record()
-    if run_steps is not None:
-        run_steps()
-    else:
-        for _ in range(args.steps):
-            step()
+    for _ in range(reps):
+        k_steps()
     ev1.record()
     barrier()
     t_wall1 = time.perf_counter()
@@ -764,7 +896,7 @@ def main():
         t = torch.tensor([ms_total], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
-    ms_per_step = ms_total / args.steps
+    ms_per_step = ms_total / (args.steps * reps)
     queries_per_step = B * H * W * world
     value = queries_per_step / (ms_per_step * 1e-3)
 
@@ -783,7 +915,7 @@ def main():
         lanes = [torch.cuda.Stream(device=dev) for _ in range(min(3, B))]
         fork, joins = torch.cuda.Event(), [torch.cuda.Event() for _ in lanes]
 
-        def e2e_step():
+        def e2e_step(with_kernel=True, with_attn=True):
             main = torch.cuda.current_stream()
             fork.record(main)
             for i in range(B):
@@ -793,32 +925,54 @@ def main():
                 with torch.cuda.stream(st):
                     for d, s in zip(d_in, host):
                         d[i:i + 1].copy_(s[i:i + 1], non_blocking=True)
-                    ma.launch(d_in[0][i:i + 1], d_in[1][i:i + 1], d_in[2][i:i + 1], d_in[3][i:i + 1], out[i:i + 1],
-                              attn[i:i + 1], H, W, (r, r), "l1_norm", wl["scale"], **knobs)
+                    if with_kernel:
+                        ma.launch(d_in[0][i:i + 1], d_in[1][i:i + 1], d_in[2][i:i + 1], d_in[3][i:i + 1], out[i:i + 1],
+                                  attn[i:i + 1] if with_attn else None, H, W, (r, r), "l1_norm", wl["scale"], **knobs)
                     host_out[i:i + 1].copy_(out[i:i + 1], non_blocking=True)
-                    host_attn[i:i + 1].copy_(attn[i:i + 1], non_blocking=True)
+                    if with_attn:
+                        host_attn[i:i + 1].copy_(attn[i:i + 1], non_blocking=True)
             for st, ev in zip(lanes, joins):
                 ev.record(st)
                 main.wait_event(ev)
 
         e2e_steps = max(3, min(args.steps, 20))
-        for _ in range(3):
-            e2e_step()
-        barrier()
-        ev0.record()
-        for _ in range(e2e_steps):
-            e2e_step()
-        ev1.record()
-        barrier()
-        ms_e2e = ev0.elapsed_time(ev1)
-        if dist is not None:
-            t = torch.tensor([ms_e2e], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_e2e = float(t.item())
-        e2e = {"value": queries_per_step / (ms_e2e / e2e_steps * 1e-3), "unit": "queries/s",
+
+        def timed_e2e(**kw):
+            for _ in range(3):
+                e2e_step(**kw)
+            barrier()
+            ev0.record()
+            for _ in range(e2e_steps):
+                e2e_step(**kw)
+            ev1.record()
+            barrier()
+            ms = ev0.elapsed_time(ev1)
+            if dist is not None:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms / e2e_steps
+
+        ms_e2e = timed_e2e()
+        ms_copy = timed_e2e(with_kernel=False)            # the same copies without the kernel: the host link's ceiling
+        ms_self = timed_e2e(with_attn=False)              # what a self-attention caller needs back: out only
+        d2h_out = host_out.numel() * host_out.element_size()
+        e2e = {"value": queries_per_step / (ms_e2e * 1e-3), "unit": "queries/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-               "ms_per_step": ms_e2e / e2e_steps, "kernel_launches_per_step": B,
+               "ms_per_step": ms_e2e, "kernel_launches_per_step": B,
+               "h2d_GBps_per_gpu": h2d / ms_e2e / 1e6, "d2h_GBps_per_gpu": d2h / ms_e2e / 1e6,
+               "copy_only": {"ms_per_step": ms_copy, "queries_per_s": queries_per_step / (ms_copy * 1e-3),
+                             "h2d_GBps_per_gpu": h2d / ms_copy / 1e6, "d2h_GBps_per_gpu": d2h / ms_copy / 1e6,
+                             "note": "the same host<->device copies with no kernel between them"},
+               "without_attn_out": {"ms_per_step": ms_self, "queries_per_s": queries_per_step / (ms_self * 1e-3),
+                                    "d2h_bytes_per_step": d2h_out,
+                                    "note": "attention weights neither written nor copied back (self-attention callers)"},
+               "host_binding": binding,
                "pipeline": f"{B} batch items over {len(lanes)} streams, pinned host buffers"}
+    shapes = None
+    if rank == 0 and not args.no_shapes and args.workload == DEFAULT_WORKLOAD:
+        peak_gbs, _ = measured_peak()
+        shapes = [time_shape(name, dev, peak_gbs) for name in SHAPE_WORKLOADS]
     if sampler:
         sampler.stop()
 
@@ -837,8 +991,11 @@ def main():
                          "algorithmic_bytes_per_query": bpq, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "kernel": ma.describe_dispatch(h, hd, r, dtype)},
             "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
-            "gpu_launches": args.steps,      # the device-resident timed region: one kernel per step
+            "timed_region": {"k_step_repeats": reps, "seconds": ms_total * 1e-3},
+            "gpu_launches": args.steps * reps,      # the device-resident timed region: one kernel per step
         }
+        if shapes is not None:
+            line["shapes"] = shapes      # the other configuration shapes, same run, same clock record
         if e2e is not None:
             line["e2e"] = e2e
         if not args.no_cpu_baseline:

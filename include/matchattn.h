@@ -222,6 +222,32 @@ MATCHATTN_API int matchattn_upsample_field(const void *field, const void *mask, 
 MATCHATTN_API int matchattn_stereo_volume(const void *correlation, void *volume, int B, int H, int W, int dtype,
                                           void *cuda_stream);
 
+/*
+ * Consistency (non-occlusion) mask of a bidirectional field, once per layer in the model:
+ * MatchAttentionLayer.consistency_mask (models/attention_blocks.py:130-138; the sampler is
+ * bilinear_sample_by_offset, utils/utils.py:39-48) as one kernel.
+ *   field      [B, H, W, 2]   (x, y) per pixel; items [0, B/2) are one view, [B/2, B) the other; B even
+ *   noc_mask   [B, H, W, 1]   written: 1 where sum_c |field_c + other_view_field_c(sampled at pixel + field)| < threshold
+ *   field_diff [B, H, W, 1]   or NULL: the sum itself (the reference does not return it; tests use it)
+ * The other view's field is sampled bilinearly with zero padding at the normalised coordinate
+ * 2*x/(W-1) - 1 rounded as the reference's tensor ops round it.  Allocates nothing.
+ */
+MATCHATTN_API int matchattn_consistency_mask(const void *field, void *noc_mask, void *field_diff,
+                                             int B, int H, int W, float threshold, int dtype, void *cuda_stream);
+
+/*
+ * From the cost volume to the initial field: local_disparity_estimator + disp_to_flow
+ * (models/cost_volume.py:123-178) as one kernel.
+ *   volume   [B, D, H, W]     softmaxed cost volume (matchattn_stereo_volume's output); B even, D >= 5
+ *   flow     [B, H, W, 2]     written: (-disp, 0) for the first B/2 items, (disp, 0) for the rest
+ *   blur_max [B, H, W]        or NULL: maximum over D of the 5-tap box average (tests)
+ *   centre   [B, H, W] int32  or NULL: first arg max, clamped to [2, D-3] (tests)
+ * disp = sum of the five probabilities around the centre, those below 1/D dropped, normalised, times
+ * their disparities.  Allocates nothing.
+ */
+MATCHATTN_API int matchattn_local_disparity(const void *volume, void *flow, void *blur_max, int *centre,
+                                            int B, int D, int H, int W, int dtype, void *cuda_stream);
+
 /* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */
 MATCHATTN_API const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned);

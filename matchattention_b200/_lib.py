@@ -14,7 +14,8 @@ LIB_PATH = os.path.join(_PKG, "lib", "libmatchattn_b200.so")
 # every symbol include/matchattn.h declares
 EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_fused_forward_ws",
            "matchattn_fused_forward_static", "matchattn_fused_forward_glue", "matchattn_upsample_field",
-           "matchattn_stereo_volume", "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
+           "matchattn_stereo_volume", "matchattn_consistency_mask", "matchattn_local_disparity",
+           "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
 
 F32, F16, BF16 = 0, 1, 2
 L1_NORM = 0
@@ -44,6 +45,10 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_upsample_field.argtypes = [_vp] * 3 + [_i] * 6 + [_vp]
     lib.matchattn_stereo_volume.restype = _i
     lib.matchattn_stereo_volume.argtypes = [_vp, _vp, _i, _i, _i, _i, _vp]
+    lib.matchattn_consistency_mask.restype = _i
+    lib.matchattn_consistency_mask.argtypes = [_vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]
+    lib.matchattn_local_disparity.restype = _i
+    lib.matchattn_local_disparity.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]
     lib.matchattn_workspace_bytes.restype = ctypes.c_size_t
     lib.matchattn_workspace_bytes.argtypes = [_i] * 9
     lib.matchattn_describe_dispatch.restype = ctypes.c_char_p

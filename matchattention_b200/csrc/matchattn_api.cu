@@ -280,6 +280,10 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     p.N = static_cast<int>(N);
     p.r = r;
     p.scale = scale;
+    {   // a power of two that both 16-bit types hold exactly as a normal number
+        int e = 0;
+        p.scale_pow2 = dtype != MATCHATTN_F32 && scale > 0.f && frexpf(scale, &e) == 0.5f && e >= -12 && e <= 15;
+    }
     p.guard = nullptr;
     p.guard_run_if = 1;
     p.sorted = nullptr;

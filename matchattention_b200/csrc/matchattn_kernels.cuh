@@ -56,6 +56,7 @@ struct Params {
     int attn_stride;         // elements between consecutive queries of attn_out (h*M by default)
     int clamp;               // non-zero: clamp the centre to [lo, hi_x] x [lo, hi_y] first, as the caller would
     float clamp_lo, clamp_hi_x, clamp_hi_y;   // bounds, already rounded to T
+    int scale_pow2;          // non-zero: 16-bit type and `scale` is a power of two that the type represents exactly
 };
 
 // torch.clamp semantics: NaN stays NaN
@@ -169,6 +170,7 @@ struct DT<float> {
     // o += a * v over the elements of one word (o points at this word's accumulators)
     static __device__ __forceinline__ void wmul(Bcast a, uint32_t vw, float *o) { o[0] = fmaf(a, __uint_as_float(vw), o[0]); }
     static __device__ __forceinline__ uint32_t pack(const float *o) { return __float_as_uint(o[0]); }
+    static __device__ __forceinline__ float unpack(uint32_t w, int) { return __uint_as_float(w); }
     // word of packed outputs times word of the gate, rounded to T
     static __device__ __forceinline__ uint32_t gate_mul(uint32_t o, uint32_t gw) { return __float_as_uint(__fmul_rn(__uint_as_float(o), __uint_as_float(gw))); }
     // attention weights live in 32-bit words holding kElemsPerWord of them ("lo" element first)
@@ -492,7 +494,8 @@ constexpr int min_blocks()
 // EXTRAS selects the build of the kernel that also honours the rarely used Params fields (sorted
 // query order, guard, clamp, gate, strided outputs); the plain build ignores them and keeps the
 // hot path free of their branches and registers.
-template <typename T, int R, int CPL, bool MULTI, bool EXTRAS>
+// POW2: the host found `scale` to be a power of two that the 16-bit type T represents exactly.
+template <typename T, int R, int CPL, bool MULTI, bool EXTRAS, bool POW2 = false>
 __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forward_kernel(const Params p)
 {
     constexpr int SIDE = 2 * R + 2, M = SIDE * SIDE;
@@ -594,8 +597,20 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
             if constexpr (MULTI) {
                 for (int o = p.lph >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
             }
-            s[j * SIDE + i] = finish_score<T>(part, p.scale);
+            s[j * SIDE + i] = POW2 ? part : finish_score<T>(part, p.scale);
         }
+    if constexpr (POW2) {
+        // The scale is a power of two that T holds exactly, so the 16-bit product round16(h * scale) is
+        // exact: two scores share one packed negate-and-round and one packed multiply (2.5 instead of 5
+        // instructions per score), with the reference's roundings unchanged.
+        const uint32_t scale_w = DT<T>::aw_bcast(p.scale);
+#pragma unroll
+        for (int m = 0; m < M; m += 2) {
+            const uint32_t pr = DT<T>::aw_mul(DT<T>::aw_from(-s[m], -s[m + 1]), scale_w);
+            s[m] = DT<T>::unpack(pr, 0);
+            s[m + 1] = DT<T>::unpack(pr, 1);
+        }
+    }
 
     // the first value taps are requested before the softmax so that their latency overlaps it
     // (two taps: measured best, more of them spill)

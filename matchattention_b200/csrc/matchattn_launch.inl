@@ -13,9 +13,13 @@ static cudaError_t launch_fast_r(const Params &p, int cpl, bool multi, dim3 grid
 {
     const bool extras = p.guard != nullptr || p.sorted != nullptr || p.gate != nullptr || p.clamp != 0 ||
                         p.out_stride != p.C || p.attn_stride != p.h * (2 * R + 2) * (2 * R + 2);
+    // power-of-two scale: a build of the plain kernel that finishes two scores per packed instruction
+    constexpr bool kCanPack = sizeof(T) == 2;
+    const bool pow2 = kCanPack && p.scale_pow2 != 0 && !extras;
 #define MA_CASE(CPL_, MULTI_)                                                              \
     if (cpl == CPL_ && multi == MULTI_) {                                                  \
         if (extras) fused_forward_kernel<T, R, CPL_, MULTI_, true><<<grid, threads, 0, stream>>>(p);   \
+        else if (pow2) fused_forward_kernel<T, R, CPL_, MULTI_, false, kCanPack><<<grid, threads, 0, stream>>>(p);  \
         else fused_forward_kernel<T, R, CPL_, MULTI_, false><<<grid, threads, 0, stream>>>(p);         \
         return cudaGetLastError();                                                         \
     }

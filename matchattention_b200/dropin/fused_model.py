@@ -14,8 +14,9 @@ module is imported here: modules are recognised by their class names):
 * ``MatchStereo.upsample_field`` (models/match_stereo.py:73-84) -> ``upsample_field``;
 * ``GlobalCorrelation.forward``, stereo branch (models/cost_volume.py:17-55):
   the masks, the two loops over the disparities, the softmax and the
-  out-of-view fill -> ``stereo_volume``; the matmul before and the local
-  disparity estimator after stay the reference's;
+  out-of-view fill -> ``stereo_volume``, the estimator after it
+  (models/cost_volume.py:123-178) -> ``local_disparity_estimator``; the matmul
+  before them stays cuBLAS;
 * ``MatchAttentionLayer.consistency_mask`` (models/attention_blocks.py:130-138)
   -> ``consistency_mask``.
 
@@ -30,61 +31,80 @@ import torch
 from .. import ops
 
 
-def _attention_forward(self, x, max_offset, noc_mask=None):
-    B, H, W, _ = x.shape
-    N = H * W
-    r = self.win_r[0]
-    x = x.view(B, N, -1)
-    if self.cross:
-        # keys/values of a view come from the other view: project once, swap the batch halves after
-        q, g = self.q(x), self.g(x)
-        k, v = self.k(x).roll(B // 2, 0), self.v(x).roll(B // 2, 0)
-        y = ops.cross_attention_core(max_offset, q, k, v, g, H, W, r, self.scale, clamp=True)
-    else:
-        if self.noc_embed:
-            x = torch.cat((x, noc_mask.view(B, N, -1)), dim=-1)
-        q, k, v = self.q(x), self.k(x), self.v(x)
-        y = ops.self_attention_core(max_offset, q, k, v, H, W, r, self.scale, clamp=True)
-    return self.proj_drop(self.proj(y)).view(B, H, W, -1)
+def _kernels(traceable: bool):
+    """The six fused steps: plain functions (eager) or their opaque custom-op forms (torch.compile)."""
+    if traceable:
+        return types.SimpleNamespace(
+            cross=ops.cross_attention_core_op, self_=ops.self_attention_core_op, upsample=ops.upsample_field_op,
+            volume=ops.stereo_volume_op, mask=ops.consistency_mask_op, disparity=ops.local_disparity_op)
+    return types.SimpleNamespace(
+        cross=ops.cross_attention_core, self_=ops.self_attention_core, upsample=ops.upsample_field,
+        volume=ops.stereo_volume, mask=ops.consistency_mask, disparity=ops.local_disparity_estimator)
 
 
-def _upsample_field(self, field, mask, factor):
-    return ops.upsample_field(field, mask, factor)
+def _make_attention_forward(kn):
+    def forward(self, x, max_offset, noc_mask=None):
+        B, H, W, _ = x.shape
+        N = H * W
+        r = self.win_r[0]
+        x = x.view(B, N, -1)
+        if self.cross:
+            # keys/values of a view come from the other view: project once, swap the batch halves after
+            q, g = self.q(x), self.g(x)
+            k, v = self.k(x).roll(B // 2, 0), self.v(x).roll(B // 2, 0)
+            y = kn.cross(max_offset, q, k, v, g, H, W, r, self.scale, True)
+        else:
+            if self.noc_embed:
+                x = torch.cat((x, noc_mask.view(B, N, -1)), dim=-1)
+            q, k, v = self.q(x), self.k(x), self.v(x)
+            y = kn.self_(max_offset, q, k, v, H, W, r, self.scale, True)
+        return self.proj_drop(self.proj(y)).view(B, H, W, -1)
+    return forward
 
 
-def _consistency_mask(self, field, A=2):
-    return ops.consistency_mask(field, float(A))
+def _make_upsample_field(kn):
+    def upsample_field(self, field, mask, factor):
+        return kn.upsample(field, mask, factor)
+    return upsample_field
 
 
-def _make_correlation_forward(reference_forward, local_disparity_estimator):
+def _make_consistency_mask(kn):
+    def consistency_mask(self, field, A=2):
+        return kn.mask(field, float(A))
+    return consistency_mask
+
+
+def _make_correlation_forward(kn, reference_forward):
     def forward(self, x, stereo=True):
         if not stereo or x.shape[2] > ops.STEREO_VOLUME_MAX_W:
             return reference_forward(x, stereo=stereo)
         x = self.norm(x)
         ref, tgt = x.chunk(2, dim=0)
         correlation = torch.matmul(self.q(ref), self.k(tgt).transpose(-2, -1)) * self.scale
-        volume = ops.stereo_volume(correlation)
-        return local_disparity_estimator(volume), volume
+        volume = kn.volume(correlation)
+        return kn.disparity(volume), volume
     return forward
 
 
 def patch_reference_model(model, *, attention: bool = True, upsample: bool = True, volume: bool = True,
-                          consistency: bool = True):
-    """Rebind the listed steps of a reference ``MatchStereo`` instance to this library's kernels."""
-    import sys
+                          consistency: bool = True, traceable: bool = False):
+    """Rebind the listed steps of a reference ``MatchStereo`` instance to this library's kernels.
+    ``traceable=True`` goes through the opaque custom-op forms so that ``torch.compile`` can trace the
+    model around them."""
+    kn = _kernels(traceable)
+    unpatch_reference_model(model)
     for m in model.modules():
         name = type(m).__name__
         if attention and name == "MatchAttention":
             if any(p > 0 for p in (m.attn_drop.p, m.proj_drop.p)) and m.training:
                 continue                                   # dropout on the attention weights: keep the reference path
-            m.forward = types.MethodType(_attention_forward, m)
+            m.forward = types.MethodType(_make_attention_forward(kn), m)
         elif upsample and name == "MatchStereo":
-            m.upsample_field = types.MethodType(_upsample_field, m)
-        elif consistency and name == "MatchAttentionLayer" and hasattr(ops, "consistency_mask"):
-            m.consistency_mask = types.MethodType(_consistency_mask, m)
+            m.upsample_field = types.MethodType(_make_upsample_field(kn), m)
+        elif consistency and name == "MatchAttentionLayer":
+            m.consistency_mask = types.MethodType(_make_consistency_mask(kn), m)
         elif volume and name == "GlobalCorrelation":
-            estimator = getattr(sys.modules[type(m).__module__], "local_disparity_estimator")
-            m.forward = types.MethodType(_make_correlation_forward(m.forward, estimator), m)
+            m.forward = types.MethodType(_make_correlation_forward(kn, m.forward), m)
     return model
 
 

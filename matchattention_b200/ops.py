@@ -296,3 +296,125 @@ def stereo_volume(correlation: torch.Tensor) -> torch.Tensor:
                                                   torch.cuda.current_stream().cuda_stream)
     _lib.check(status)
     return vol
+
+
+def consistency_mask(field: torch.Tensor, threshold: float = 2.0, return_diff: bool = False):
+    """Same argument and result as ``MatchAttentionLayer.consistency_mask(field, A)``
+    (models/attention_blocks.py:130-138): field [B,H,W,2] (two views stacked on the batch) ->
+    noc_mask [B,H,W,1], one kernel.  ``return_diff`` also returns the thresholded quantity."""
+    if not field.is_cuda:
+        raise RuntimeError("matchattn_b200 runs on CUDA tensors only (no CPU fallback); got device " + str(field.device))
+    if field.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {field.dtype}")
+    if field.dim() != 4 or field.size(-1) != 2 or field.size(0) % 2:
+        raise ValueError("expected field [B,H,W,2] with an even batch (two views)")
+    field = field.contiguous()
+    B, H, W, _ = field.shape
+    mask = field.new_empty(B, H, W, 1)
+    diff = field.new_empty(B, H, W, 1) if return_diff else None
+    with torch.cuda.device(field.device):
+        status = _lib.lib.matchattn_consistency_mask(field.data_ptr(), mask.data_ptr(),
+                                                     diff.data_ptr() if return_diff else None, B, H, W,
+                                                     float(threshold), _DTYPE_CODE[field.dtype],
+                                                     torch.cuda.current_stream().cuda_stream)
+    _lib.check(status)
+    return (mask, diff) if return_diff else mask
+
+
+def local_disparity_estimator(volume: torch.Tensor, return_debug: bool = False):
+    """Same argument and result as ``local_disparity_estimator(cv)`` (models/cost_volume.py:123-167, with
+    disp_to_flow :169-178): cost volume [B,D,H,W] -> field [B,H,W,2], one kernel.  ``return_debug``
+    also returns the blurred maximum [B,H,W] and the window centre [B,H,W] (int32)."""
+    if not volume.is_cuda:
+        raise RuntimeError("matchattn_b200 runs on CUDA tensors only (no CPU fallback); got device " + str(volume.device))
+    if volume.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {volume.dtype}")
+    if volume.dim() != 4 or volume.size(0) % 2 or volume.size(1) < 5:
+        raise ValueError("expected volume [B,D,H,W] with an even batch (two views) and D >= 5")
+    vol = volume.contiguous()
+    B, D, H, W = vol.shape
+    flow = vol.new_empty(B, H, W, 2)
+    blur = vol.new_empty(B, H, W) if return_debug else None
+    centre = torch.empty(B, H, W, dtype=torch.int32, device=vol.device) if return_debug else None
+    with torch.cuda.device(vol.device):
+        status = _lib.lib.matchattn_local_disparity(vol.data_ptr(), flow.data_ptr(),
+                                                    blur.data_ptr() if return_debug else None,
+                                                    centre.data_ptr() if return_debug else None, B, D, H, W,
+                                                    _DTYPE_CODE[vol.dtype], torch.cuda.current_stream().cuda_stream)
+    _lib.check(status)
+    return (flow, blur, centre) if return_debug else flow
+
+
+# ---- the fused steps as opaque custom ops ------------------------------------------------------
+# torch.compile cannot trace a ctypes call.  These wrappers give the compiler the same thing the
+# reference gives it for its own extension (models/match_former_ops.py:6-62): an opaque op with a fake
+# kernel that only states shapes and dtypes.  Eager callers should keep using the plain functions
+# above (one Python dispatch less per call).
+
+@torch.library.custom_op("matchattn_b200::cross_attention_core_op", mutates_args=())
+def cross_attention_core_op(max_offset: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                            gate: torch.Tensor, H: int, W: int, r: int, scale: float, clamp: bool) -> torch.Tensor:
+    return cross_attention_core(max_offset.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(),
+                                gate.contiguous(), H, W, r, scale, clamp)
+
+
+@cross_attention_core_op.register_fake
+def _(max_offset, q, k, v, gate, H, W, r, scale, clamp):
+    B, N, C = q.shape
+    return q.new_empty(B, N, C + max_offset.size(2) * (2 * r + 2) ** 2)
+
+
+@torch.library.custom_op("matchattn_b200::self_attention_core_op", mutates_args=())
+def self_attention_core_op(max_offset: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                           H: int, W: int, r: int, scale: float, clamp: bool) -> torch.Tensor:
+    return self_attention_core(max_offset.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), H, W, r,
+                               scale, clamp)
+
+
+@self_attention_core_op.register_fake
+def _(max_offset, q, k, v, H, W, r, scale, clamp):
+    return torch.empty_like(q, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("matchattn_b200::upsample_field_op", mutates_args=())
+def upsample_field_op(field: torch.Tensor, mask: torch.Tensor, factor: int) -> torch.Tensor:
+    return upsample_field(field, mask, factor)
+
+
+@upsample_field_op.register_fake
+def _(field, mask, factor):
+    B, H, W, D = field.shape
+    return field.new_empty(B, H * factor, W * factor, D)
+
+
+@torch.library.custom_op("matchattn_b200::stereo_volume_op", mutates_args=())
+def stereo_volume_op(correlation: torch.Tensor) -> torch.Tensor:
+    return stereo_volume(correlation)
+
+
+@stereo_volume_op.register_fake
+def _(correlation):
+    B, H, W, _ = correlation.shape
+    return correlation.new_empty(2 * B, W, H, W)
+
+
+@torch.library.custom_op("matchattn_b200::consistency_mask_op", mutates_args=())
+def consistency_mask_op(field: torch.Tensor, threshold: float) -> torch.Tensor:
+    return consistency_mask(field, threshold)
+
+
+@consistency_mask_op.register_fake
+def _(field, threshold):
+    B, H, W, _ = field.shape
+    return field.new_empty(B, H, W, 1)
+
+
+@torch.library.custom_op("matchattn_b200::local_disparity_op", mutates_args=())
+def local_disparity_op(volume: torch.Tensor) -> torch.Tensor:
+    return local_disparity_estimator(volume)
+
+
+@local_disparity_op.register_fake
+def _(volume):
+    B, D, H, W = volume.shape
+    return volume.new_empty(B, H, W, 2)

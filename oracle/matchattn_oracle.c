@@ -420,3 +420,112 @@ int matchattn_oracle_stereo_volume(const void *corr, void *volume, int B, int H,
     free(sm);
     return 0;
 }
+
+/*
+ * Consistency (non-occlusion) mask, MatchAttentionLayer.consistency_mask
+ * (models/attention_blocks.py:130-138 with utils/utils.py:31-48):
+ *   field [B, H, W, 2] (x, y), the first B/2 items one view, the last B/2 the other;
+ *   offset   = field + pixel grid
+ *   sampled  = bilinear sample (align_corners, zero padding) of the OTHER view's field at offset,
+ *              through normalised coordinates 2*x/(W-1) - 1 as the reference computes them
+ *   diff     = sum_c |field_c + sampled_c|
+ *   mask     = diff < A
+ * Rounding model of the 16-bit types: every elementwise tensor op rounds to the tensor type; the
+ * sampler itself works in float32 from the rounded normalised coordinate (as PyTorch's CUDA
+ * grid sampler does) and rounds its result once.  diff_out (may be NULL) receives diff.
+ */
+int matchattn_oracle_consistency_mask(const void *field, void *mask_out, void *diff_out, int B, int H, int W,
+                                      float A, int dtype)
+{
+    if (!field || !mask_out) return 1;
+    if (B <= 0 || (B & 1) || H <= 1 || W <= 1) return 2;
+    if (dtype != MA_F32 && dtype != MA_F16 && dtype != MA_BF16) return 4;
+    ensure_half_table();
+    const int dt = dtype;
+    for (int b = 0; b < B; ++b) {
+        const int tb = (b + B / 2) % B;
+        for (int y = 0; y < H; ++y)
+            for (int x = 0; x < W; ++x) {
+                const int64_t px = ((int64_t)b * H + y) * W + x;
+                const float f0 = load_elem(field, px * 2, dt), f1 = load_elem(field, px * 2 + 1, dt);
+                const float ox = RND(f0 + (float)x), oy = RND(f1 + (float)y);
+                const float gx = RND(RND(RND(2.0f * ox) / (float)(W - 1)) - 1.0f);
+                const float gy = RND(RND(RND(2.0f * oy) / (float)(H - 1)) - 1.0f);
+                const float ix = ((gx + 1.0f) / 2.0f) * (float)(W - 1), iy = ((gy + 1.0f) / 2.0f) * (float)(H - 1);
+                const float fx0 = floorf(ix), fy0 = floorf(iy);
+                const float wx1 = ix - fx0, wx0 = (fx0 + 1.0f) - ix, wy1 = iy - fy0, wy0 = (fy0 + 1.0f) - iy;
+                const float wgt[4] = { wx0 * wy0, wx1 * wy0, wx0 * wy1, wx1 * wy1 };
+                float diff = 0.0f;
+                for (int c = 0; c < 2; ++c) {
+                    float acc = 0.0f;
+                    for (int t = 0; t < 4; ++t) {
+                        const float cx = fx0 + (float)(t & 1), cy = fy0 + (float)(t >> 1);
+                        if (cx >= 0.0f && cx <= (float)(W - 1) && cy >= 0.0f && cy <= (float)(H - 1))
+                            acc = fmaf(load_elem(field, ((((int64_t)tb * H + (int)cy) * W) + (int)cx) * 2 + c, dt), wgt[t], acc);
+                    }
+                    const float sampled = RND(acc);
+                    diff += fabsf(RND((c == 0 ? f0 : f1) + sampled));
+                }
+                diff = RND(diff);
+                if (diff_out) store_elem(diff_out, px, diff, dt);
+                store_elem(mask_out, px, diff < A ? 1.0f : 0.0f, dt);
+            }
+    }
+    return 0;
+}
+
+/*
+ * Local disparity estimator, local_disparity_estimator + disp_to_flow (models/cost_volume.py:123-178):
+ *   cv [B, D, H, W] (softmaxed cost volume) -> flow [B, H, W, 2].
+ *   blur   = 5-tap box average over D (zero padded, always divided by 5)
+ *   centre = first arg max of blur over D, clamped to [2, D-3]
+ *   p_k    = cv at centre-2 .. centre+2, zeroed where below 1/D, normalised by their sum
+ *            (sum floored at the smallest normal number of the tensor type)
+ *   disp   = sum_k p_k * (centre - 2 + k); negated for the first B/2 items; flow = (disp, 0).
+ * blur_out / centre_out (may be NULL) receive the blurred maximum and the clamped centre: the tests
+ * gate the discrete choice on them.  below_exact = 1 compares p < 1/D with 1/D in float32 (PyTorch on
+ * the GPU), 0 with 1/D rounded to the tensor type (PyTorch on the CPU).
+ */
+int matchattn_oracle_local_disparity(const void *cv, void *flow, void *blur_out, int *centre_out, int B, int D, int H,
+                                     int W, int dtype, int below_exact)
+{
+    if (!cv || !flow) return 1;
+    if (B <= 0 || (B & 1) || D < 5 || H <= 0 || W <= 0) return 2;
+    if (dtype != MA_F32 && dtype != MA_F16 && dtype != MA_BF16) return 4;
+    ensure_half_table();
+    const int dt = dtype;
+    const int64_t plane = (int64_t)H * W;
+    const float tiny = dt == MA_F32 ? 1.17549435e-38f : (dt == MA_F16 ? 6.103515625e-05f : 1.17549435e-38f);
+    const float mean = below_exact ? (float)(1.0 / D) : RND((float)(1.0 / D));
+    for (int b = 0; b < B; ++b)
+        for (int64_t px = 0; px < plane; ++px) {
+            const int64_t base = (int64_t)b * D * plane + px;
+            float best = -INFINITY;
+            int arg = 0;
+            for (int d = 0; d < D; ++d) {
+                float acc = 0.0f;
+                for (int t = d - 2; t <= d + 2; ++t)
+                    if (t >= 0 && t < D) acc += load_elem(cv, base + (int64_t)t * plane, dt);
+                const float bl = RND(acc / 5.0f);
+                if (bl > best) { best = bl; arg = d; }
+            }
+            int centre = arg < 2 ? 2 : (arg > D - 3 ? D - 3 : arg);
+            float p[5], sum = 0.0f;
+            for (int t = 0; t < 5; ++t) {
+                p[t] = load_elem(cv, base + (int64_t)(centre - 2 + t) * plane, dt);
+                if (p[t] < mean) p[t] = 0.0f;
+                sum += p[t];
+            }
+            sum = RND(sum);
+            if (sum < tiny) sum = tiny;
+            float disp = 0.0f;
+            for (int t = 0; t < 5; ++t) disp += RND(RND(p[t] / sum) * RND((float)(centre - 2 + t)));
+            disp = RND(disp);
+            if (b < B / 2) disp = -disp;
+            store_elem(flow, ((int64_t)b * plane + px) * 2, disp, dt);
+            store_elem(flow, ((int64_t)b * plane + px) * 2 + 1, 0.0f, dt);
+            if (blur_out) store_elem(blur_out, (int64_t)b * plane + px, best, dt);
+            if (centre_out) centre_out[(int64_t)b * plane + px] = centre;
+        }
+    return 0;
+}

@@ -34,6 +34,27 @@ def golden_names(pattern="*"):
                                                   "flowinit_"))]
 
 
+def load_golden_arrays(name):
+    """A golden file as a dict of torch tensors (16-bit arrays viewed in the file's dtype) and scalars."""
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    dt = DTYPES[str(z["dtype"])]
+    out = {"dtype": dt}
+    for key in z.files:
+        if key in ("dtype", "note"):
+            continue
+        a = z[key]
+        if a.ndim == 0:
+            out[key] = a.item()
+            continue
+        t = torch.from_numpy(a.copy())
+        out[key] = t.view(torch.bfloat16) if (dt == torch.bfloat16 and t.dtype == torch.int16) else t
+    return out
+
+
+def golden_names_with_prefix(prefix):
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, prefix + "*.npz")))
+
+
 def golden_sampled_names():
     return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "sampled_*.npz")))
 
@@ -110,15 +131,15 @@ def excess(got, ref, dtype):
     return float((err / allowed).max()) if err.numel() else 0.0
 
 
-# Rounding ties.  A 16-bit score is the float32 channel sum rounded to 16 bits.  When that sum lies
-# within a few float32 ulps of a 16-bit rounding boundary, the order of the additions decides which
-# way it rounds, and every implementation (eager PyTorch on CPU, on GPU, the oracle, the kernel)
-# adds in a different order.  One such flip moves a logit by one 16-bit ulp of the score (up to 0.06
-# for the 80-wide heads) and with it all outputs of that (query, head).  The strict gate therefore
-# holds for the narrow heads of the headline shapes, where the sums are exact in float32; for wide
-# heads a small fraction of elements may exceed it by a bounded factor.
-TIE_FRACTION = 1e-3
-TIE_FACTOR = 15.0
+# Rounding ties.  A 16-bit score is the float32 channel sum rounded to 16 bits; implementations add in
+# different orders, so a sum that lies within a few float32 ulps of a 16-bit rounding boundary could
+# round differently.  Measured on a B200 against the oracle (which is bit-compatible with the
+# reference's CPU path on these shapes): over 13 wide-head shapes (head widths 24 to 256, r 1 and 2,
+# 4 seeds each, about 9e7 outputs per type) not one element of `out` or `attn` exceeded the strict gate
+# in float16 or bfloat16, the worst being one 16-bit ulp.  The `ties` flag of assert_close is therefore
+# kept only as a name at the call sites of the wide-head cases: it grants nothing.
+TIE_FRACTION = 0.0
+TIE_FACTOR = 1.0
 
 
 def assert_close(got, ref, dtype, what="", ties=False):

@@ -241,6 +241,49 @@ def volume_cases(ref_root):
             print(f"{name}_{tag}: {os.path.getsize(path) / 1024:.0f} KiB")
 
 
+def field_op_cases(ref_root, blocks):
+    """MatchAttentionLayer.consistency_mask (models/attention_blocks.py:130-138) and
+    local_disparity_estimator (models/cost_volume.py:123-178) on seeded inputs.  Besides the reference's
+    outputs the files hold the continuous quantity behind each discrete decision (the thresholded
+    field difference; the gap between the best and the second-best blurred probability), so that a test
+    can gate the decision only where it is not a tie."""
+    from models.cost_volume import local_disparity_estimator
+    from utils.utils import bilinear_sample_by_offset, init_coords
+    import torch.nn.functional as F
+    tags = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}
+    for name, seed, B, H, W, amp in (("consistency_a", 71, 2, 11, 14, 2.5), ("consistency_b", 72, 4, 9, 23, 6.0)):
+        gen = torch.Generator().manual_seed(seed)
+        field32 = torch.randn(B, H, W, 2, generator=gen) * amp
+        for dtype in tags:
+            field = field32.to(dtype)
+            mask = blocks.MatchAttentionLayer.consistency_mask(None, field)
+            # the quantity the reference thresholds (same statements, models/attention_blocks.py:131-136)
+            offset = field + init_coords(field)
+            a, b = field.chunk(2, dim=0)
+            tgt = torch.cat((b, a), dim=0)
+            warped = bilinear_sample_by_offset(tgt.permute(0, 3, 1, 2).contiguous(), offset).permute(0, 2, 3, 1)
+            diff = torch.abs(field + warped).sum(dim=-1, keepdim=True)
+            path = os.path.join(HERE, f"{name}_{tags[dtype]}.npz")
+            np.savez_compressed(path, dtype=str(dtype).replace("torch.", ""), field=to_np(field), mask=to_np(mask),
+                                diff=to_np(diff.contiguous()), threshold=2.0,
+                                note=f"seed {seed}, MatchAttentionLayer.consistency_mask of the reference on CPU")
+            print(f"{name}_{tags[dtype]}: {os.path.getsize(path) / 1024:.0f} KiB")
+    for name, seed, B, D, H, W, sharp in (("disparity_a", 81, 2, 24, 7, 24, 3.0), ("disparity_b", 82, 4, 40, 5, 40, 1.0)):
+        gen = torch.Generator().manual_seed(seed)
+        vol32 = torch.softmax(torch.randn(B, D, H, W, generator=gen) * sharp, dim=1)
+        for dtype in tags:
+            vol = vol32.to(dtype)
+            flow = local_disparity_estimator(vol.clone())
+            blur = F.avg_pool1d(vol.permute(0, 2, 3, 1).reshape(B, -1, D), kernel_size=5, stride=1, padding=2)
+            top2 = blur.float().topk(2, dim=-1).values
+            path = os.path.join(HERE, f"{name}_{tags[dtype]}.npz")
+            np.savez_compressed(path, dtype=str(dtype).replace("torch.", ""), volume=to_np(vol), flow=to_np(flow),
+                                blur_max=to_np(blur.max(-1).values.view(B, H, W).contiguous()),
+                                gap=(top2[..., 0] - top2[..., 1]).view(B, H, W).numpy(),
+                                note=f"seed {seed}, local_disparity_estimator of the reference on CPU")
+            print(f"{name}_{tags[dtype]}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF"), required="MATCHATTN_REF" not in os.environ,
@@ -248,9 +291,13 @@ def main():
     ap.add_argument("--skip-model", action="store_true")
     ap.add_argument("--only-upsample", action="store_true", help="regenerate only the upsample_field vectors")
     ap.add_argument("--only-new", action="store_true", help="only the wide-head and sampled full-size operator vectors")
+    ap.add_argument("--only-field-ops", action="store_true", help="only the consistency-mask and disparity vectors")
     a = ap.parse_args()
     impl, blocks = import_reference(a.ref)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if a.only_field_ops:
+        field_op_cases(a.ref, blocks)
+        return
     if a.only_new:
         wide_head_cases(impl, blocks)
         sampled_full_size_cases(impl)
@@ -263,6 +310,7 @@ def main():
             model_cases(a.ref, impl)
     upsample_cases(a.ref)
     volume_cases(a.ref)
+    field_op_cases(a.ref, blocks)
 
 
 if __name__ == "__main__":
