@@ -253,86 +253,39 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def run_band_mode(args, rank, local_rank, world):
-    """One very large pair split by query row bands (strong scaling): rank 0 owns q/k/v/max_offset,
-    K and V are broadcast over NCCL, every rank runs the kernel on its band, outputs return to rank 0."""
-    import torch.distributed as dist
+def measure_band(rank, world, dev, dist, steps=10, warmup=3):
+    """One very large pair split by query row bands (strong scaling): 1024x1024 tokens (a 4096x4096 pair at
+    1/4 resolution), B=2 views, 4 heads x 32, float16, smooth flow of at most 32 tokens.  Three ways of getting
+    K/V to the ranks, each timed on the device (max over ranks) against the same call on one GPU:
+      source_broadcast    rank 0 owns everything: NCCL broadcast of K and V, band inputs scattered, band
+                          outputs gathered every step (the form the specification of this mode names)
+      resident_allgather  every rank holds its own rows of q/max_offset/K/V and keeps its rows of the outputs:
+                          K/V rows all-gathered every step
+      resident_halo       same, but only the rows a band can reach (|dy| <= 33 rows) move between neighbours
+    Returns the dict that goes into the JSON line (on rank 0; None elsewhere)."""
     import matchattention_b200 as ma
-    from matchattention_b200.band import band_match_attention, band_rows
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    B, H, W, h, hd, r, dtype = 2, 1024, 1024, 4, 32, 1, torch.float16      # a 4096x4096 pair at 1/4 resolution
-    N, C = H * W, h * hd
-    kv = [torch.empty(B, N, C, dtype=dtype, device=dev) for _ in range(2)]
-    full = (None, None, None, None)
-    if rank == 0:
-        g = torch.Generator(device=dev).manual_seed(99)
-        q, k, v = (torch.randn(B, N, C, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(3))
-        ys, xs = torch.meshgrid(torch.arange(H, device=dev, dtype=torch.float32),
-                                torch.arange(W, device=dev, dtype=torch.float32), indexing="ij")
-        # smooth flow of at most 32 tokens (128 px): low-resolution noise, bilinearly upsampled
-        coarse = (torch.rand(B, 2, 9, 9, generator=g, device=dev) * 2 - 1) * 32.0
-        flow = torch.nn.functional.interpolate(coarse, size=(H, W), mode="bilinear", align_corners=True)
-        mo = torch.stack((xs + flow[:, 0], ys + flow[:, 1]), dim=-1).view(B, N, 1, 2).expand(B, N, h, 2)
-        mo = torch.cat((mo[..., :1].clamp(r, W - 1 - r - 1e-3), mo[..., 1:].clamp(r, H - 1 - r - 1e-3)), -1)
-        full = (mo.to(dtype).contiguous(), q, k, v)
-
-    from matchattention_b200.band import halo_rows
-    max_dy = 33.0 if args.band_kv == "halo" else None       # the synthetic flow is at most 32 tokens
+    from matchattention_b200.band import (band_match_attention, band_match_attention_resident, band_rows, halo_rows)
+    B, H, W, h, hd, r, dtype = 2, 1024, 1024, 4, 32, 1, torch.float16
+    N, C, M = H * W, h * hd, 16
+    scale = hd ** -0.5
+    # the same seeded tensors on every rank (generated on the device), so that any rank can slice its band
+    g = torch.Generator(device=dev).manual_seed(99)
+    q, k, v = (torch.randn(B, N, C, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(3))
+    ys, xs = torch.meshgrid(torch.arange(H, device=dev, dtype=torch.float32),
+                            torch.arange(W, device=dev, dtype=torch.float32), indexing="ij")
+    coarse = (torch.rand(B, 2, 9, 9, generator=g, device=dev) * 2 - 1) * 32.0
+    flow = torch.nn.functional.interpolate(coarse, size=(H, W), mode="bilinear", align_corners=True)
+    mo = torch.stack((xs + flow[:, 0], ys + flow[:, 1]), dim=-1).view(B, N, 1, 2).expand(B, N, h, 2)
+    mo = torch.cat((mo[..., :1].clamp(r, W - 1 - r - 1e-3), mo[..., 1:].clamp(r, H - 1 - r - 1e-3)), -1).to(dtype).contiguous()
+    del ys, xs, flow, coarse
     r0, r1 = band_rows(H, world, rank)
-
-    # resident variant: every rank already holds its band of q / max_offset and keeps its band of the
-    # outputs (what a band-parallel caller would do); only K and V move each step
-    if args.band_resident and world > 1:
-        q_band = torch.empty(B, (r1 - r0) * W, C, dtype=dtype, device=dev)
-        mo_band = torch.empty(B, (r1 - r0) * W, h, 2, dtype=dtype, device=dev)
-        if rank == 0:
-            for pr in range(1, world):
-                p0, p1 = band_rows(H, world, pr)
-                dist.send(full[1][:, p0 * W:p1 * W].contiguous(), pr)
-                dist.send(full[0][:, p0 * W:p1 * W].contiguous(), pr)
-            q_band.copy_(full[1][:, r0 * W:r1 * W])
-            mo_band.copy_(full[0][:, r0 * W:r1 * W])
-            kv = [full[2], full[3]]
-        else:
-            dist.recv(q_band, 0)
-            dist.recv(mo_band, 0)
-        out_band = torch.empty_like(q_band)
-        attn_band = q_band.new_empty(B, (r1 - r0) * W, h, 16)
-
-    def replicate_kv():
-        if max_dy is None:
-            dist.broadcast(kv[0], src=0)
-            dist.broadcast(kv[1], src=0)
-        elif rank == 0:
-            ops, keep = [], []
-            for pr in range(1, world):
-                p0, p1 = band_rows(H, world, pr)
-                h0, h1 = halo_rows(H, p0, p1, r, max_dy)
-                for t in kv:
-                    keep.append(t[:, h0 * W:h1 * W].contiguous())
-                    ops.append(dist.P2POp(dist.isend, keep[-1], pr))
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()
-        else:
-            h0, h1 = halo_rows(H, r0, r1, r, max_dy)
-            parts = [torch.empty(B, (h1 - h0) * W, C, dtype=dtype, device=dev) for _ in kv]
-            for req in dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, 0) for t in parts]):
-                req.wait()
-            kv[0][:, h0 * W:h1 * W] = parts[0]
-            kv[1][:, h0 * W:h1 * W] = parts[1]
-
-    def step():
-        if world == 1:
-            return ma.match_attention(*full, H, W, r, hd ** -0.5)
-        if args.band_resident:
-            replicate_kv()
-            return ma.match_attention(mo_band, q_band, kv[0], kv[1], H, W, r, hd ** -0.5, q_row_begin=r0,
-                                      q_row_end=r1, out=out_band, attn_out=attn_band)
-        return band_match_attention(*full, B, H, W, h, hd, r, hd ** -0.5, dtype, dev, kv_buffers=kv,
-                                    max_abs_dy=max_dy)
+    sl = slice(r0 * W, r1 * W)
+    bands = [t[:, sl].contiguous() for t in (mo, q)]
+    # resident layout: full-size K/V buffers in which only this rank's own rows are valid on entry
+    kv_full = [torch.full_like(k, float("nan")), torch.full_like(v, float("nan"))]
+    kv_full[0][:, sl], kv_full[1][:, sl] = k[:, sl], v[:, sl]
+    out_band, attn_band = torch.empty_like(bands[1]), q.new_empty(B, (r1 - r0) * W, h, M)
+    max_dy = 33.0
 
     def barrier():
         torch.cuda.synchronize()
@@ -340,29 +293,76 @@ def run_band_mode(args, rank, local_rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
+    def timed(fn, n=steps):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / n
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    full_out, full_attn = torch.empty_like(q), q.new_empty(B, N, h, M)
+    one_gpu = timed(lambda: ma.match_attention(mo, q, k, v, H, W, r, scale, out=full_out, attn_out=full_attn))
+    res = {"workload": "op_1024x1024_b2_h4x32_r1_f16_rowband", "one_gpu_ms": one_gpu, "n_gpus": world,
+           "kv_bytes": 2 * B * N * C * 2, "variants": {}}
     if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
+        src_args = (mo, q, k, v) if rank == 0 else (None, None, None, None)
+        kv_recv = [k, v] if rank == 0 else kv_full
+        esz = 2
+        variants = {
+            "source_broadcast": (lambda: band_match_attention(*src_args, B, H, W, h, hd, r, scale, dtype, dev,
+                                                              kv_buffers=kv_recv),
+                                 2 * B * N * C * esz),
+            "resident_allgather": (lambda: band_match_attention_resident(*bands, *kv_full, H, W, r, scale,
+                                                                         out=out_band, attn_out=attn_band),
+                                   2 * B * (N - (r1 - r0) * W) * C * esz),
+            "resident_halo": (lambda: band_match_attention_resident(*bands, *kv_full, H, W, r, scale,
+                                                                    out=out_band, attn_out=attn_band, max_abs_dy=max_dy),
+                              2 * B * ((lambda hr: (hr[1] - hr[0]) - (r1 - r0))(halo_rows(H, r0, r1, r, max_dy))) * W * C * esz),
+        }
+        for name, (fn, recv_bytes) in variants.items():
+            ms = timed(fn)
+            res["variants"][name] = {"ms": ms, "speedup_vs_one_gpu": one_gpu / ms,
+                                     "kv_bytes_received_per_rank": recv_bytes,
+                                     "kv_receive_GBps_if_exchange_were_all": recv_bytes / ms / 1e6}
+        # the resident forms must reproduce the one-GPU result on the band
+        for t, src in zip(kv_full, (k, v)):        # back to "only my rows are valid" before the check
+            t.fill_(float("nan"))
+            t[:, sl] = src[:, sl]
+        band_match_attention_resident(*bands, *kv_full, H, W, r, scale, out=out_band, attn_out=attn_band,
+                                      max_abs_dy=max_dy)
+        ok = torch.tensor([int(torch.equal(out_band, full_out[:, sl]) and torch.equal(attn_band, full_attn[:, sl]))],
+                          device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        res["bands_bit_identical_to_one_gpu"] = bool(ok.item())
+        best = min(res["variants"].items(), key=lambda kv_: kv_[1]["ms"])
+        res["best"] = {"variant": best[0], "ms": best[1]["ms"], "speedup_vs_one_gpu": best[1]["speedup_vs_one_gpu"]}
+    return res if rank == 0 else None
+
+
+def run_band_mode(args, rank, local_rank, world):
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    res = measure_band(rank, world, dev, dist, steps=max(3, min(args.steps, 20)), warmup=max(3, min(args.warmup, 5)))
     if rank == 0:
-        line = {"metric": "matchattention_queries_per_s", "value": B * N / (ms_per_step * 1e-3), "unit": "queries/s",
-                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": "op_1024x1024_b2_h4x32_r1_f16_rowband",
-                           "mode": f"row bands, K/V {args.band_kv}" + (", q/out bands resident" if args.band_resident else ", q scattered and out gathered every step"),
-                           "kv_broadcast_bytes_per_step": 2 * B * N * C * 2, "band_rows": band_rows(H, world, 0)},
-                "gpu_launches": args.steps}
+        ms = res["best"]["ms"] if world > 1 else res["one_gpu_ms"]
+        line = {"metric": "matchattention_queries_per_s", "value": 2 * 1024 * 1024 / (ms * 1e-3), "unit": "queries/s",
+                "n_gpus": world, "steps": max(3, min(args.steps, 20)), "warmup": max(3, min(args.warmup, 5)),
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+                "data": "synthetic", "config": {"workload": res["workload"], "mode": "row bands"}, "band": res,
+                "gpu_launches": max(3, min(args.steps, 20))}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -585,6 +585,7 @@ def run_model_mode(args):
         except Exception as exc:          # a step of the model that cannot be captured
             notes["fused_graph"] = "not captured: " + str(exc).splitlines()[0][:200]
             torch.cuda.synchronize()
+        compiled_field = None
         if args.model_compile:
             # torch.compile around the opaque ops, as the reference's own driver compiles its model
             # (run_img.py:55-58: default mode, dynamic=False, TF32 matmuls allowed)
@@ -597,6 +598,7 @@ def run_model_mode(args):
                 torch.cuda.synchronize()
                 notes["fused_compiled_compile_s"] = round(time.perf_counter() - t0, 1)
                 parity["fused_compiled_field_up_rel"] = rel(got["field_up"], want["field_up"])
+                compiled_field = got["field_up"].clone()
                 arms["fused_compiled"] = timed(lambda: cmodel(left, right, stereo=stereo))
                 try:
                     with torch.cuda.stream(side):
@@ -619,9 +621,14 @@ def run_model_mode(args):
                 ref_model = build("pytorch")
                 cref = torch.compile(ref_model, dynamic=False)
                 t0 = time.perf_counter()
-                cref(left, right, stereo=stereo)
+                want_compiled = cref(left, right, stereo=stereo)
                 torch.cuda.synchronize()
                 notes["pytorch_compiled_compile_s"] = round(time.perf_counter() - t0, 1)
+                # compilation itself changes the rounding (TF32 matmuls, float32 intermediates inside fused
+                # kernels): the reference's compiled model against its own eager run, and ours against it
+                parity["pytorch_compiled_vs_pytorch_eager_field_up_rel"] = rel(want_compiled["field_up"], want["field_up"])
+                if compiled_field is not None:
+                    parity["fused_compiled_vs_pytorch_compiled_field_up_rel"] = rel(compiled_field, want_compiled["field_up"])
                 arms["pytorch_compiled"] = timed(lambda: cref(left, right, stereo=stereo))
             except Exception as exc:
                 notes["pytorch_compiled"] = "failed: " + str(exc).splitlines()[0][:300]
@@ -771,10 +778,7 @@ def main():
     ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
-    ap.add_argument("--band-kv", choices=["broadcast", "halo"], default="broadcast",
-                    help="band mode: replicate all of K/V (NCCL broadcast) or only the rows a band can reach")
-    ap.add_argument("--band-resident", action="store_true",
-                    help="band mode: q / max_offset / outputs stay distributed, only K/V move each step")
+    ap.add_argument("--no-band", action="store_true", help="with more than one GPU: skip the row-band measurement")
     ap.add_argument("--model-variant", default="tiny", choices=["tiny", "small", "base"])
     ap.add_argument("--model-size", type=int, nargs=2, default=[1536, 1536], metavar=("H", "W"))
     ap.add_argument("--model-dtype", default="f16", choices=["f16", "bf16", "f32"])
@@ -969,6 +973,11 @@ def main():
                                     "note": "attention weights neither written nor copied back (self-attention callers)"},
                "host_binding": binding,
                "pipeline": f"{B} batch items over {len(lanes)} streams, pinned host buffers"}
+    band = None
+    if world > 1 and not args.no_band and args.workload == DEFAULT_WORKLOAD:
+        del host_out, host_attn, d_in
+        torch.cuda.empty_cache()
+        band = measure_band(rank, world, dev, dist)
     shapes = None
     if rank == 0 and not args.no_shapes and args.workload == DEFAULT_WORKLOAD:
         peak_gbs, _ = measured_peak()
@@ -991,9 +1000,15 @@ def main():
                          "algorithmic_bytes_per_query": bpq, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "kernel": ma.describe_dispatch(h, hd, r, dtype)},
             "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
-            "timed_region": {"k_step_repeats": reps, "seconds": ms_total * 1e-3},
+            "timed_region": {"k_step_repeats": reps, "seconds": ms_total * 1e-3,
+                             "first_k_steps_ms_per_step": once_ms / args.steps,
+                             "note": "value and ms_per_step are the mean over the whole region; first_k_steps is the "
+                                     "K steps timed once beforehand (a burst of a few milliseconds, before the "
+                                     "power cap lowers the SM clock; see clocks)"},
             "gpu_launches": args.steps * reps,      # the device-resident timed region: one kernel per step
         }
+        if band is not None:
+            line["band"] = band          # one huge pair split by query row bands over the same GPUs (strong scaling)
         if shapes is not None:
             line["shapes"] = shapes      # the other configuration shapes, same run, same clock record
         if e2e is not None:

@@ -248,6 +248,24 @@ MATCHATTN_API int matchattn_consistency_mask(const void *field, void *noc_mask, 
 MATCHATTN_API int matchattn_local_disparity(const void *volume, void *flow, void *blur_max, int *centre,
                                             int B, int D, int H, int W, int dtype, void *cuda_stream);
 
+/*
+ * Flow branch of GlobalCorrelation after its matmul, with local_flow_estimator
+ * (models/cost_volume.py:61-69 and :71-121): the step before the first MatchAttention block of MatchFlow.
+ *   correlation [B, N, N]      N = H*W; scaled q.k^T, reference token then target token
+ *   prob        [2B, N, N]     written: softmax over the last axis of correlation[b] (items [0, B)) and of its
+ *                              transpose (items [B, 2B)); the reference returns it viewed as [2B, H, W, N]
+ *   flow        [2B, H, W, 2]  written: expected target position within the 5x5 window around the arg max of the
+ *                              5x5-pooled probabilities, minus the token's own position
+ *   blur_max    [2B, N]        or NULL: the pooled maximum (tests)
+ *   centre      [2B, N] int32  or NULL: the clamped window centre as y*W + x (tests)
+ *   scratch     at least matchattn_flow_init_scratch_bytes(B, H, W) bytes of device memory, 16-byte aligned
+ * H, W >= 5.  Allocates nothing; five kernels on `cuda_stream`.
+ */
+MATCHATTN_API size_t matchattn_flow_init_scratch_bytes(int B, int H, int W);
+MATCHATTN_API int matchattn_flow_init(const void *correlation, void *prob, void *flow, void *blur_max, int *centre,
+                                      void *scratch, size_t scratch_bytes, int B, int H, int W, int dtype,
+                                      void *cuda_stream);
+
 /* Name of the kernel variant the arguments would dispatch to ("fast cpl=2 lph=1",
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */
 MATCHATTN_API const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned);

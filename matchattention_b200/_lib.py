@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libmatchattn_b200.so")
 EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_fused_forward_ws",
            "matchattn_fused_forward_static", "matchattn_fused_forward_glue", "matchattn_upsample_field",
            "matchattn_stereo_volume", "matchattn_consistency_mask", "matchattn_local_disparity",
+           "matchattn_flow_init", "matchattn_flow_init_scratch_bytes",
            "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
 
 F32, F16, BF16 = 0, 1, 2
@@ -49,6 +50,10 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_consistency_mask.argtypes = [_vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]
     lib.matchattn_local_disparity.restype = _i
     lib.matchattn_local_disparity.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]
+    lib.matchattn_flow_init_scratch_bytes.restype = ctypes.c_size_t
+    lib.matchattn_flow_init_scratch_bytes.argtypes = [_i, _i, _i]
+    lib.matchattn_flow_init.restype = _i
+    lib.matchattn_flow_init.argtypes = [_vp] * 6 + [ctypes.c_size_t, _i, _i, _i, _i, _vp]
     lib.matchattn_workspace_bytes.restype = ctypes.c_size_t
     lib.matchattn_workspace_bytes.argtypes = [_i] * 9
     lib.matchattn_describe_dispatch.restype = ctypes.c_char_p

@@ -9,6 +9,21 @@ memory, and the kernel then reads them with ordinary loads.  The band inputs
 (q, max_offset) travel to their rank and the band outputs come back to the
 source rank with point-to-point copies.
 
+Two forms:
+
+* :func:`band_match_attention` -- one rank owns q/k/v/max_offset (the form the specification of
+  this mode names): K and V are broadcast from it, the band inputs travel to their rank and the
+  band outputs come back.  Everything that moves leaves or enters the owner's links, so this form
+  cannot be faster than the owner computing alone (measured; see the benchmark's ``band`` object).
+* :func:`band_match_attention_resident` -- every rank already holds ITS rows of q, max_offset, K and
+  V (the state of a pipeline whose producers are band-parallel too) and keeps its rows of the
+  outputs.  K/V rows are exchanged with an all-gather, or, when the caller can bound how far a
+  centre lies from its query row, only the halo rows move between neighbouring ranks.
+
+:func:`band_check` is the CPU-side handshake to run before either form when the ranks' arguments
+come from different code paths: it fails on every rank if one rank reports an error or the
+arguments differ, and -- given a process group with a short timeout -- when a rank never arrives.
+
 The reference has no multi-GPU code; this is the partition its operator admits.
 One process per GPU; `torch.distributed` must be initialised by the caller.
 """
@@ -162,3 +177,110 @@ def band_match_attention(max_offset: Optional[torch.Tensor], q: Optional[torch.T
         if need_attn:
             attn[:, p0 * W:p1 * W] = ab
     return out, attn
+
+
+class BandArgumentError(RuntimeError):
+    """Raised on every rank by :func:`band_check` when the ranks disagree or one of them failed."""
+
+
+def band_check(B: int, H: int, W: int, h: int, hd: int, r: int, dtype: torch.dtype, *, group=None,
+               error: Optional[BaseException] = None) -> None:
+    """Host-side handshake before a band call (no device work, nothing enqueued on a stream).
+
+    Every rank contributes the arguments it is about to use and, if its own preparation failed, the
+    error (pass the exception instead of raising it, so that the rank still takes part).  If any
+    rank reports an error or the arguments differ, EVERY rank raises BandArgumentError before any
+    collective on device data starts.  A rank that died or never calls makes the others' gather fail
+    once the process group's timeout expires: create the group with a short timeout
+    (``dist.new_group(timeout=...)`` / ``init_process_group(timeout=...)``) to bound that wait.
+    """
+    world = dist.get_world_size(group)
+    mine = {"args": (B, H, W, h, hd, r, str(dtype)), "error": None if error is None else f"{type(error).__name__}: {error}"}
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine, group=group)
+    failed = [(p, e["error"]) for p, e in enumerate(everyone) if e["error"] is not None]
+    if failed:
+        raise BandArgumentError("rank(s) failed before the band call: " + "; ".join(f"rank {p}: {e}" for p, e in failed))
+    if any(e["args"] != everyone[0]["args"] for e in everyone):
+        raise BandArgumentError("ranks disagree on the band call's arguments: "
+                                + "; ".join(f"rank {p}: {e['args']}" for p, e in enumerate(everyone)))
+
+
+def _exchange_rows(fulls: List[torch.Tensor], H: int, W: int, r: int, world: int, rank: int, group,
+                   max_abs_dy: Optional[float], peer) -> None:
+    """Complete the [B, H*W, C] buffers `fulls` in place.  On entry each holds this rank's own rows
+    [r0, r1); on return it also holds every other rank's rows (all-gather) or, with `max_abs_dy`, the
+    rows this rank's band can reach (halo rows from the neighbouring ranks).  Rows move straight between
+    the buffers, item by item (an item's rows are contiguous): no staging copies."""
+    if world == 1:
+        return
+    B = fulls[0].size(0)
+    r0, r1 = band_rows(H, world, rank)
+    if max_abs_dy is None and H % world == 0 and fulls[0].is_cuda:
+        for full in fulls:                         # in-place all-gather: the input is the output's own slice
+            for b in range(B):
+                dist.all_gather_into_tensor(full[b], full[b, r0 * W:r1 * W], group=group)
+        return
+    ops = []
+    for p in range(world):
+        if p == rank:
+            continue
+        p0, p1 = band_rows(H, world, p)
+        if max_abs_dy is None:
+            need_me, need_p = (r0, r1), (p0, p1)   # uneven bands (or a CPU group): every band to every rank
+        else:
+            h0, h1 = halo_rows(H, p0, p1, r, max_abs_dy)
+            need_me = (max(h0, r0), min(h1, r1))   # rows of mine that p can reach
+            g0, g1 = halo_rows(H, r0, r1, r, max_abs_dy)
+            need_p = (max(g0, p0), min(g1, p1))    # rows of p that I can reach
+        for full in fulls:
+            for b in range(B):
+                if need_me[1] > need_me[0]:
+                    ops.append(dist.P2POp(dist.isend, full[b, need_me[0] * W:need_me[1] * W], peer(p), group))
+                if need_p[1] > need_p[0]:
+                    ops.append(dist.P2POp(dist.irecv, full[b, need_p[0] * W:need_p[1] * W], peer(p), group))
+    _p2p(ops)
+
+
+def band_match_attention_resident(mo_band: torch.Tensor, q_band: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                                  H: int, W: int, r: int, scale: float, *, group=None, need_attn: bool = True,
+                                  op: Optional[Callable] = None, kv_full=None, max_abs_dy: Optional[float] = None,
+                                  out=None, attn_out=None):
+    """One MatchAttention call over row bands that already live on their ranks.
+
+    Every rank passes ITS rows [r0, r1) = band_rows(H, world, rank) of max_offset [B,rows*W,h,2] and of
+    q [B,rows*W,C], and gets back its rows of (out, attn).  Keys and values come in one of two layouts:
+
+    * resident (no copies): `k` and `v` are full-size [B,H*W,C] buffers in which this rank's producer
+      has written its own rows in place; the other rows are scratch that this call fills;
+    * bands: `k` and `v` are [B,rows*W,C]; they are first copied into `kv_full` (a pair of full-size
+      buffers, allocated when None and reusable between calls).
+
+    The missing rows arrive by an all-gather of the bands or -- with `max_abs_dy`, the caller's bound in
+    rows on |centre_y - query row| -- only the halo rows each band can reach travel between neighbouring
+    ranks; rows outside stay untouched and are never read.  The kernel follows on the rank's own stream.
+    """
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    op = op or _default_op
+    B, _, C = q_band.shape
+    r0, r1 = band_rows(H, world, rank)
+    if k.size(1) == H * W and (world == 1 or r1 - r0 != H):
+        fulls = [k, v]                              # resident layout
+    else:
+        if kv_full is None:
+            kv_full = [torch.empty((B, H * W, C), dtype=q_band.dtype, device=q_band.device) for _ in range(2)]
+        fulls = list(kv_full)
+        fulls[0][:, r0 * W:r1 * W] = k
+        fulls[1][:, r0 * W:r1 * W] = v
+
+    def peer(p):
+        return dist.get_global_rank(group, p) if group is not None else p
+
+    _exchange_rows(fulls, H, W, r, world, rank, group, max_abs_dy, peer)
+    if r1 == r0:
+        return None, None
+    if op is _default_op:
+        from .ops import match_attention
+        return match_attention(mo_band, q_band, fulls[0], fulls[1], H, W, r, scale, need_attn=need_attn,
+                               q_row_begin=r0, q_row_end=r1, out=out, attn_out=attn_out)
+    return op(mo_band, q_band, fulls[0], fulls[1], H, W, r, scale, r0, r1, need_attn)

@@ -88,8 +88,8 @@ __global__ void __launch_bounds__(128) local_disparity_kernel(const T *__restric
         w0 = w1; w1 = w2; w2 = w3; w3 = w4;
     }
     const int centre = min(max(arg, 2), D - 3);
-    // PyTorch compares the 16-bit probabilities with 1/D as a float32 scalar on the GPU
-    const float mean = static_cast<float>(1.0 / static_cast<double>(D));
+    // PyTorch converts the scalar 1/D to the tensor type before it compares
+    const float mean = DT<T>::rnd(static_cast<float>(1.0 / static_cast<double>(D)));
     float p[5], sum = 0.f;
 #pragma unroll
     for (int t = 0; t < 5; ++t) {

@@ -579,8 +579,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     uint32_t qw[NW];
     load_words<NW>(qw, static_cast<const T *>(p.q) + bq * p.C + lane_off);
 
-    // scores
+    // scores.  With a power-of-two scale that T holds exactly (POW2), round16(h * scale) is an exact
+    // 16-bit product: two neighbouring taps share one packed negate-and-round and one packed multiply,
+    // and the finished scores stay packed (eight registers instead of sixteen) until the softmax, which
+    // leaves room for one more tap load in flight.  The roundings are the reference's either way.
     float s[M];
+    uint32_t sp[POW2 ? M / 2 : 1];
+    float part_even = 0.f;
 #pragma unroll
     for (int j = 0; j < SIDE; ++j)
 #pragma unroll
@@ -597,18 +602,18 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
             if constexpr (MULTI) {
                 for (int o = p.lph >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
             }
-            s[j * SIDE + i] = POW2 ? part : finish_score<T>(part, p.scale);
+            if constexpr (POW2) {
+                if (i & 1) sp[(j * SIDE + i) >> 1] = DT<T>::aw_mul(DT<T>::aw_from(-part_even, -part), DT<T>::aw_bcast(p.scale));
+                else part_even = part;
+            } else {
+                s[j * SIDE + i] = finish_score<T>(part, p.scale);
+            }
         }
     if constexpr (POW2) {
-        // The scale is a power of two that T holds exactly, so the 16-bit product round16(h * scale) is
-        // exact: two scores share one packed negate-and-round and one packed multiply (2.5 instead of 5
-        // instructions per score), with the reference's roundings unchanged.
-        const uint32_t scale_w = DT<T>::aw_bcast(p.scale);
 #pragma unroll
         for (int m = 0; m < M; m += 2) {
-            const uint32_t pr = DT<T>::aw_mul(DT<T>::aw_from(-s[m], -s[m + 1]), scale_w);
-            s[m] = DT<T>::unpack(pr, 0);
-            s[m + 1] = DT<T>::unpack(pr, 1);
+            s[m] = DT<T>::unpack(sp[m >> 1], 0);
+            s[m + 1] = DT<T>::unpack(sp[m >> 1], 1);
         }
     }
 

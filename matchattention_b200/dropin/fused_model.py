@@ -15,7 +15,8 @@ module is imported here: modules are recognised by their class names):
 * ``GlobalCorrelation.forward``, stereo branch (models/cost_volume.py:17-55):
   the masks, the two loops over the disparities, the softmax and the
   out-of-view fill -> ``stereo_volume``, the estimator after it
-  (models/cost_volume.py:123-178) -> ``local_disparity_estimator``; the matmul
+  (models/cost_volume.py:123-178) -> ``local_disparity_estimator``; the flow
+  branch (:56-69 with local_flow_estimator :71-121) -> ``flow_init``; the matmul
   before them stays cuBLAS;
 * ``MatchAttentionLayer.consistency_mask`` (models/attention_blocks.py:130-138)
   -> ``consistency_mask``.
@@ -36,10 +37,12 @@ def _kernels(traceable: bool):
     if traceable:
         return types.SimpleNamespace(
             cross=ops.cross_attention_core_op, self_=ops.self_attention_core_op, upsample=ops.upsample_field_op,
-            volume=ops.stereo_volume_op, mask=ops.consistency_mask_op, disparity=ops.local_disparity_op)
+            volume=ops.stereo_volume_op, mask=ops.consistency_mask_op, disparity=ops.local_disparity_op,
+            flow_init=ops.flow_init_op)
     return types.SimpleNamespace(
         cross=ops.cross_attention_core, self_=ops.self_attention_core, upsample=ops.upsample_field,
-        volume=ops.stereo_volume, mask=ops.consistency_mask, disparity=ops.local_disparity_estimator)
+        volume=ops.stereo_volume, mask=ops.consistency_mask, disparity=ops.local_disparity_estimator,
+        flow_init=ops.flow_init)
 
 
 def _make_attention_forward(kn):
@@ -76,13 +79,19 @@ def _make_consistency_mask(kn):
 
 def _make_correlation_forward(kn, reference_forward):
     def forward(self, x, stereo=True):
-        if not stereo or x.shape[2] > ops.STEREO_VOLUME_MAX_W:
+        B2, H, W, C = x.shape
+        if (stereo and W > ops.STEREO_VOLUME_MAX_W) or (not stereo and (H < 5 or W < 5)):
             return reference_forward(x, stereo=stereo)
         x = self.norm(x)
         ref, tgt = x.chunk(2, dim=0)
-        correlation = torch.matmul(self.q(ref), self.k(tgt).transpose(-2, -1)) * self.scale
-        volume = kn.volume(correlation)
-        return kn.disparity(volume), volume
+        ref, tgt = self.q(ref), self.k(tgt)
+        if stereo:
+            correlation = torch.matmul(ref, tgt.transpose(-2, -1)) * self.scale
+            volume = kn.volume(correlation)
+            return kn.disparity(volume), volume
+        correlation = torch.matmul(ref.reshape(B2 // 2, H * W, C), tgt.reshape(B2 // 2, H * W, C).transpose(-2, -1)) * self.scale
+        flow, prob = kn.flow_init(correlation, H, W)
+        return flow, prob
     return forward
 
 

@@ -345,6 +345,34 @@ def local_disparity_estimator(volume: torch.Tensor, return_debug: bool = False):
     return (flow, blur, centre) if return_debug else flow
 
 
+def flow_init(correlation: torch.Tensor, H: int, W: int, return_debug: bool = False):
+    """What GlobalCorrelation.forward does after its matmul when ``stereo=False`` (models/cost_volume.py:61-69,
+    with local_flow_estimator :71-121): correlation [B,N,N] (N = H*W) -> (flow [2B,H,W,2], prob [2B,H,W,N]).
+    ``return_debug`` adds the pooled maximum [2B,N] and the clamped window centre [2B,N] (int32)."""
+    if not correlation.is_cuda:
+        raise RuntimeError("matchattn_b200 runs on CUDA tensors only (no CPU fallback); got device "
+                           + str(correlation.device))
+    if correlation.dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {correlation.dtype}")
+    if correlation.dim() != 3 or correlation.size(1) != H * W or correlation.size(2) != H * W:
+        raise ValueError("expected correlation [B, H*W, H*W]")
+    corr = correlation.contiguous()
+    B, N, _ = corr.shape
+    prob = corr.new_empty(2 * B, H, W, N)
+    flow = corr.new_empty(2 * B, H, W, 2)
+    blur = corr.new_empty(2 * B, N) if return_debug else None
+    centre = torch.empty(2 * B, N, dtype=torch.int32, device=corr.device) if return_debug else None
+    nbytes = int(_lib.lib.matchattn_flow_init_scratch_bytes(B, H, W))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=corr.device)
+    with torch.cuda.device(corr.device):
+        status = _lib.lib.matchattn_flow_init(corr.data_ptr(), prob.data_ptr(), flow.data_ptr(),
+                                              blur.data_ptr() if return_debug else None,
+                                              centre.data_ptr() if return_debug else None, scratch.data_ptr(), nbytes,
+                                              B, H, W, _DTYPE_CODE[corr.dtype], torch.cuda.current_stream().cuda_stream)
+    _lib.check(status)
+    return (flow, prob, blur, centre) if return_debug else (flow, prob)
+
+
 # ---- the fused steps as opaque custom ops ------------------------------------------------------
 # torch.compile cannot trace a ctypes call.  These wrappers give the compiler the same thing the
 # reference gives it for its own extension (models/match_former_ops.py:6-62): an opaque op with a fake
@@ -418,3 +446,14 @@ def local_disparity_op(volume: torch.Tensor) -> torch.Tensor:
 def _(volume):
     B, D, H, W = volume.shape
     return volume.new_empty(B, H, W, 2)
+
+
+@torch.library.custom_op("matchattn_b200::flow_init_op", mutates_args=())
+def flow_init_op(correlation: torch.Tensor, H: int, W: int) -> List[torch.Tensor]:
+    return list(flow_init(correlation, H, W))
+
+
+@flow_init_op.register_fake
+def _(correlation, H, W):
+    B, N, _ = correlation.shape
+    return [correlation.new_empty(2 * B, H, W, 2), correlation.new_empty(2 * B, H, W, N)]

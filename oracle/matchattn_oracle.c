@@ -483,11 +483,10 @@ int matchattn_oracle_consistency_mask(const void *field, void *mask_out, void *d
  *            (sum floored at the smallest normal number of the tensor type)
  *   disp   = sum_k p_k * (centre - 2 + k); negated for the first B/2 items; flow = (disp, 0).
  * blur_out / centre_out (may be NULL) receive the blurred maximum and the clamped centre: the tests
- * gate the discrete choice on them.  below_exact = 1 compares p < 1/D with 1/D in float32 (PyTorch on
- * the GPU), 0 with 1/D rounded to the tensor type (PyTorch on the CPU).
+ * gate the discrete choice on them.
  */
 int matchattn_oracle_local_disparity(const void *cv, void *flow, void *blur_out, int *centre_out, int B, int D, int H,
-                                     int W, int dtype, int below_exact)
+                                     int W, int dtype)
 {
     if (!cv || !flow) return 1;
     if (B <= 0 || (B & 1) || D < 5 || H <= 0 || W <= 0) return 2;
@@ -496,7 +495,7 @@ int matchattn_oracle_local_disparity(const void *cv, void *flow, void *blur_out,
     const int dt = dtype;
     const int64_t plane = (int64_t)H * W;
     const float tiny = dt == MA_F32 ? 1.17549435e-38f : (dt == MA_F16 ? 6.103515625e-05f : 1.17549435e-38f);
-    const float mean = below_exact ? (float)(1.0 / D) : RND((float)(1.0 / D));
+    const float mean = RND((float)(1.0 / D));      /* PyTorch converts the scalar to the tensor type before comparing */
     for (int b = 0; b < B; ++b)
         for (int64_t px = 0; px < plane; ++px) {
             const int64_t base = (int64_t)b * D * plane + px;
@@ -527,5 +526,88 @@ int matchattn_oracle_local_disparity(const void *cv, void *flow, void *blur_out,
             if (blur_out) store_elem(blur_out, (int64_t)b * plane + px, best, dt);
             if (centre_out) centre_out[(int64_t)b * plane + px] = centre;
         }
+    return 0;
+}
+
+/*
+ * Flow branch of GlobalCorrelation with its estimator (models/cost_volume.py:56-69 and
+ * local_flow_estimator :71-121), from the scaled all-pairs correlation to the initial flow:
+ *   corr [B, N, N], N = H*W (reference token, then target token)
+ *   prob [2B, N, N]   prob[b] = softmax over the last axis of corr[b], prob[B+b] = the same of corr[b]^T
+ *   blur  = 5x5 box average of prob[b2] taken as an N x N IMAGE (zero padded, divided by 25): the reference
+ *           applies avg_pool2d to the 3-D tensor, so the window runs over neighbouring reference AND target
+ *           token indices (models/cost_volume.py:86)
+ *   centre = first arg max of blur over the target axis, as (y, x) = (idx / W, idx % W), clamped to
+ *            [2, H-3] x [2, W-3]
+ *   p_k   = prob at the 5x5 tokens around the centre, zeroed where below 1/N, normalised by their sum
+ *           (floored at the smallest normal number of the type)
+ *   flow  = sum_k p_k * (x_k, y_k) - (x, y) of the reference token
+ * blur_max_out [2B, N] and centre_out [2B, N] (flat target index after the clamp) may be NULL.
+ */
+int matchattn_oracle_flow_init(const void *corr, void *prob, void *flow, void *blur_max_out, int *centre_out,
+                               int B, int H, int W, int dtype)
+{
+    if (!corr || !prob || !flow) return 1;
+    if (B <= 0 || H < 5 || W < 5) return 2;
+    if (dtype != MA_F32 && dtype != MA_F16 && dtype != MA_BF16) return 4;
+    ensure_half_table();
+    const int dt = dtype;
+    const int64_t N = (int64_t)H * W;
+    const float tiny = dt == MA_F16 ? 6.103515625e-05f : 1.17549435e-38f;
+    const float mean = RND((float)(1.0 / (double)N));
+    float *row = (float *)malloc(sizeof(float) * (size_t)N);
+    if (!row) return 2;
+    /* softmax of every row of corr[b] and of corr[b]^T */
+    for (int b2 = 0; b2 < 2 * B; ++b2) {
+        const int tr = b2 >= B, b = tr ? b2 - B : b2;
+        for (int64_t i = 0; i < N; ++i) {
+            float mx = -INFINITY, den = 0.0f;
+            for (int64_t j = 0; j < N; ++j) {
+                row[j] = load_elem(corr, (int64_t)b * N * N + (tr ? j * N + i : i * N + j), dt);
+                mx = row[j] > mx ? row[j] : mx;
+            }
+            for (int64_t j = 0; j < N; ++j) { row[j] = expf(row[j] - mx); den += row[j]; }
+            for (int64_t j = 0; j < N; ++j) store_elem(prob, ((int64_t)b2 * N + i) * N + j, row[j] / den, dt);
+        }
+    }
+    for (int b2 = 0; b2 < 2 * B; ++b2)
+        for (int64_t i = 0; i < N; ++i) {
+            const int64_t pb = (int64_t)b2 * N * N;
+            float best = -INFINITY;
+            int64_t arg = 0;
+            for (int64_t j = 0; j < N; ++j) {
+                float acc = 0.0f;
+                for (int64_t ii = i - 2; ii <= i + 2; ++ii)
+                    for (int64_t jj = j - 2; jj <= j + 2; ++jj)
+                        if (ii >= 0 && ii < N && jj >= 0 && jj < N) acc += load_elem(prob, pb + ii * N + jj, dt);
+                const float bl = RND(acc / 25.0f);
+                if (bl > best) { best = bl; arg = j; }
+            }
+            int cy = (int)(arg / W), cx = (int)(arg % W);
+            cy = cy < 2 ? 2 : (cy > H - 3 ? H - 3 : cy);
+            cx = cx < 2 ? 2 : (cx > W - 3 ? W - 3 : cx);
+            float p[25], sum = 0.0f;
+            for (int t = 0; t < 25; ++t) {
+                const int sy = cy + t / 5 - 2, sx = cx + t % 5 - 2;
+                p[t] = load_elem(prob, pb + i * N + (int64_t)sy * W + sx, dt);
+                if (p[t] < mean) p[t] = 0.0f;
+                sum += p[t];
+            }
+            sum = RND(sum);
+            if (sum < tiny) sum = tiny;
+            float ax = 0.0f, ay = 0.0f;
+            for (int t = 0; t < 25; ++t) {
+                const int sy = cy + t / 5 - 2, sx = cx + t % 5 - 2;
+                const float np_ = RND(p[t] / sum);
+                ax += RND(np_ * RND((float)sx));
+                ay += RND(np_ * RND((float)sy));
+            }
+            const int qy = (int)(i / W), qx = (int)(i % W);
+            store_elem(flow, ((int64_t)b2 * N + i) * 2, RND(RND(ax) - RND((float)qx)), dt);
+            store_elem(flow, ((int64_t)b2 * N + i) * 2 + 1, RND(RND(ay) - RND((float)qy)), dt);
+            if (blur_max_out) store_elem(blur_max_out, (int64_t)b2 * N + i, best, dt);
+            if (centre_out) centre_out[(int64_t)b2 * N + i] = cy * W + cx;
+        }
+    free(row);
     return 0;
 }

@@ -284,6 +284,34 @@ def field_op_cases(ref_root, blocks):
             print(f"{name}_{tags[dtype]}: {os.path.getsize(path) / 1024:.0f} KiB")
 
 
+def flow_init_cases(ref_root):
+    """GlobalCorrelation.forward with stereo=False (models/cost_volume.py:56-69, local_flow_estimator :71-121):
+    the scaled correlation the module computes (recomputed here with its own layers) and what it returns."""
+    from models.cost_volume import GlobalCorrelation
+    import torch.nn.functional as F
+    tags = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}
+    for name, seed, B, H, W, C, gain in (("flowinit_a", 91, 1, 6, 7, 16, 6.0), ("flowinit_b", 92, 2, 5, 9, 8, 12.0)):
+        torch.manual_seed(seed)
+        mod = GlobalCorrelation(C).eval()
+        x32 = torch.randn(2 * B, H, W, C) * gain
+        for dtype in tags:
+            m, x = mod.to(dtype), x32.to(dtype)
+            with torch.inference_mode():
+                xn = m.norm(x)
+                ref, tgt = xn.chunk(2, dim=0)
+                corr = torch.matmul(m.q(ref).view(B, -1, C), m.k(tgt).view(B, -1, C).transpose(-2, -1)) * m.scale
+                flow, prob = m(x, stereo=False)
+                blur = F.avg_pool2d(prob.view(2 * B, H * W, H * W), kernel_size=5, stride=1, padding=2)
+            top2 = blur.float().topk(2, dim=-1).values
+            path = os.path.join(HERE, f"{name}_{tags[dtype]}.npz")
+            np.savez_compressed(path, dtype=str(dtype).replace("torch.", ""), H=H, W=W,
+                                correlation=to_np(corr.contiguous()), flow=to_np(flow.contiguous()),
+                                prob=to_np(prob.contiguous()), blur_max=to_np(blur.max(-1).values.contiguous()),
+                                gap=(top2[..., 0] - top2[..., 1]).numpy(),
+                                note=f"seed {seed}, GlobalCorrelation(dim={C}) of the reference on CPU, stereo=False")
+            print(f"{name}_{tags[dtype]}: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF"), required="MATCHATTN_REF" not in os.environ,
@@ -297,6 +325,7 @@ def main():
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     if a.only_field_ops:
         field_op_cases(a.ref, blocks)
+        flow_init_cases(a.ref)
         return
     if a.only_new:
         wide_head_cases(impl, blocks)
@@ -311,6 +340,7 @@ def main():
     upsample_cases(a.ref)
     volume_cases(a.ref)
     field_op_cases(a.ref, blocks)
+    flow_init_cases(a.ref)
 
 
 if __name__ == "__main__":

@@ -98,3 +98,114 @@ def test_band_split_with_halo_exchange():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert results.get(timeout=5) == (True, True)
+
+
+# ---- the resident form: every rank holds its own rows of q / max_offset / K / V -------------------------
+
+def _resident_worker(rank, world, port, H, W, results, max_abs_dy, in_place):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from _cases import make_inputs
+        from matchattention_b200.band import band_match_attention_resident, band_rows
+        B, h, hd, r = 2, 2, 8, 1
+        mo, q, k, v = make_inputs(33, B, H, W, h, hd, r, torch.float16, kind="flow", spread=4.0,
+                                  border_frac=0.1 if max_abs_dy is None else 0.0)       # same on every rank (seeded)
+        r0, r1 = band_rows(H, world, rank)
+        sl = slice(r0 * W, r1 * W)
+
+        def op(mo_b, q_b, kk, vv, H_, W_, r_, scale, a, b, need_attn):
+            return oracle.forward(mo_b, q_b, kk, vv, H_, W_, r_, scale, q_row_begin=a, q_row_end=b, nthreads=1,
+                                  want_attn=need_attn)
+
+        kv = [torch.full((B, H * W, h * hd), float("nan"), dtype=torch.float16) for _ in range(2)]
+        if in_place:      # resident layout: the rank's own rows already sit in the full-size buffers
+            kv[0][:, sl], kv[1][:, sl] = k[:, sl], v[:, sl]
+            kin, vin = kv
+        else:
+            kin, vin = k[:, sl].contiguous(), v[:, sl].contiguous()
+        out, attn = band_match_attention_resident(mo[:, sl].contiguous(), q[:, sl].contiguous(), kin, vin, H, W, r, 0.3,
+                                                  op=op, kv_full=kv, max_abs_dy=max_abs_dy)
+        ref_out, ref_attn = oracle.forward(mo, q, k, v, H, W, r, 0.3, nthreads=1)
+        ok = r1 == r0 or (bool(torch.equal(out, ref_out[:, sl])) and bool(torch.equal(attn, ref_attn[:, sl])))
+        if max_abs_dy is None:
+            ok = ok and bool(torch.equal(kv[0], k)) and bool(torch.equal(kv[1], v))
+        results.put(ok)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("in_place", [False, True], ids=["bands", "resident"])
+@pytest.mark.parametrize("world,H,dy", [(2, 10, None), (3, 10, None), (3, 30, 4.0), (4, 16, None)])
+def test_resident_bands_equal_the_full_result(world, H, dy, in_place):
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = 29500 + (os.getpid() + 31 * world + H + 500 * in_place) % 2000
+    procs = [ctx.Process(target=_resident_worker, args=(rank, world, port, H, 8, results, dy, in_place))
+             for rank in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(results.get(timeout=5) for _ in range(world))
+
+
+# ---- failure paths, all on the host: nothing here faults, traps or hangs a device ------------------------
+
+def _failure_worker(rank, world, port, scenario, results):
+    import datetime
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=6))
+    from matchattention_b200.band import BandArgumentError, band_check
+    verdict = "no error"
+    try:
+        if scenario == "rank_raises":
+            # rank 1 fails while preparing its inputs: it reports the error instead of vanishing
+            err = ValueError("could not load my band") if rank == 1 else None
+            band_check(2, 16, 8, 2, 8, 1, torch.float16, error=err)
+        elif scenario == "shape_mismatch":
+            band_check(2, 16 if rank == 0 else 18, 8, 2, 8, 1, torch.float16)
+        elif scenario == "rank_absent":
+            if rank == 1:
+                results.put((rank, "left"))
+                return                            # never joins the handshake (the process exits between steps)
+            band_check(2, 16, 8, 2, 8, 1, torch.float16)
+    except BandArgumentError as exc:
+        verdict = "BandArgumentError: " + str(exc)
+    except Exception as exc:                      # the process group's timeout or the peer's closed connection
+        verdict = "transport error: " + type(exc).__name__
+    results.put((rank, verdict))
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+@pytest.mark.parametrize("scenario", ["rank_raises", "shape_mismatch", "rank_absent"])
+def test_band_failures_are_detected_on_the_host(scenario):
+    import time
+    world = 2
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = 29500 + (os.getpid() + 611 + len(scenario)) % 2000
+    procs = [ctx.Process(target=_failure_worker, args=(rank, world, port, scenario, results)) for rank in range(world)]
+    t0 = time.time()
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode is not None, "a rank hung instead of failing"
+    got = dict(results.get(timeout=5) for _ in range(world))
+    assert time.time() - t0 < 60
+    if scenario == "rank_raises":
+        assert all(v.startswith("BandArgumentError") and "could not load my band" in v for v in got.values()), got
+    elif scenario == "shape_mismatch":
+        assert all(v.startswith("BandArgumentError") and "disagree" in v for v in got.values()), got
+    else:
+        assert got[1] == "left" and got[0].startswith("transport error"), got

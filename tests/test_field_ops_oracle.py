@@ -34,8 +34,7 @@ def test_consistency_mask_oracle_matches_reference_vectors(name):
 def test_local_disparity_oracle_matches_reference_vectors(name):
     c = load_golden_arrays(name)
     dt = c["dtype"]
-    # PyTorch's CPU build compares the probabilities with 1/D rounded to the tensor type
-    flow, blur, centre = oracle.local_disparity(c["volume"], below_exact=False)
+    flow, blur, centre = oracle.local_disparity(c["volume"])
     assert (flow[..., 1] == 0).all()
     if dt == torch.float32:
         assert (blur - c["blur_max"]).abs().max() <= 1e-6
@@ -70,3 +69,23 @@ def test_consistency_mask_of_consistent_fields():
     mask, diff = oracle.consistency_mask(field)
     assert (diff[0, :, 2:] == 0).all() and (mask[0, :, 2:] == 1).all()
     assert (diff[0, :, :2] == 2).all() and (mask[0, :, :2] == 0).all()      # sampled outside: zero padding
+
+
+@pytest.mark.parametrize("name", golden_names_with_prefix("flowinit_"))
+def test_flow_init_oracle_matches_reference_vectors(name):
+    """GlobalCorrelation's flow branch + local_flow_estimator: probabilities within one 16-bit ulp (1e-6 in
+    float32), the pooled maximum likewise, the flow wherever the arg max is not a tie."""
+    c = load_golden_arrays(name)
+    dt, H, W = c["dtype"], c["H"], c["W"]
+    flow, prob, blur, centre = oracle.flow_init(c["correlation"], H, W)
+    if dt == torch.float32:
+        assert (prob - c["prob"]).abs().max() <= 1e-6 and (blur - c["blur_max"]).abs().max() <= 1e-6
+    else:
+        assert ((prob.float() - c["prob"].float()).abs() <= ulp16(c["prob"].float(), dt)).all()
+        assert ((blur.float() - c["blur_max"].float()).abs() <= ulp16(c["blur_max"].float(), dt)).all()
+    clear = (c["gap"] > (1e-6 if dt == torch.float32 else 0.0)).view(-1, H, W)
+    assert clear.float().mean() > 0.5
+    err = (flow.float() - c["flow"].float()).abs()[clear]
+    ref = c["flow"].float()[clear]
+    allowed = 1e-4 * ref.abs().clamp_min(1.0) if dt == torch.float32 else 2 * ulp16(ref.abs().clamp_min(1.0), dt)
+    assert (err <= allowed).all(), f"{name}: flow off by {err.max():.4g}"

@@ -53,7 +53,7 @@ def test_local_disparity_kernel_matches_oracle(name):
     import oracle
     c = load_golden_arrays(name)
     dt = c["dtype"]
-    want_flow, want_blur, want_centre = oracle.local_disparity(c["volume"], below_exact=True)
+    want_flow, want_blur, want_centre = oracle.local_disparity(c["volume"])
     flow, blur, centre = _ma().local_disparity_estimator(c["volume"].cuda(), return_debug=True)
     torch.cuda.synchronize()
     assert _close16(blur, want_blur, dt)
@@ -100,3 +100,43 @@ def test_local_disparity_kernel_matches_reference_on_the_gpu(dtype):
     assert clear.float().mean() > 0.5
     assert _close16(flow[..., 0][clear], want[..., 0][clear], dtype)
     assert (flow[..., 1] == 0).all()
+
+
+@pytest.mark.parametrize("name", golden_names_with_prefix("flowinit_"))
+def test_flow_init_kernels_match_oracle(name):
+    import oracle
+    c = load_golden_arrays(name)
+    dt, H, W = c["dtype"], c["H"], c["W"]
+    want_flow, want_prob, want_blur, want_centre = oracle.flow_init(c["correlation"], H, W)
+    flow, prob, blur, centre = _ma().flow_init(c["correlation"].cuda(), H, W, return_debug=True)
+    torch.cuda.synchronize()
+    assert _close16(prob, want_prob, dt) and _close16(blur, want_blur, dt)
+    clear = c["gap"] > (1e-6 if dt == torch.float32 else 0.0)
+    assert torch.equal(centre.cpu()[clear], want_centre[clear])
+    assert _close16(flow.cpu().view(-1, H * W, 2)[clear], want_flow.view(-1, H * W, 2)[clear], dt, ulps=2.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,W", [(12, 16), (9, 37)])
+def test_flow_init_kernels_match_reference_on_the_gpu(dtype, H, W):
+    """The reference's GlobalCorrelation.forward(stereo=False) on the same GPU against the kernels, fed with
+    the correlation the module itself computes."""
+    _reference()
+    from models.cost_volume import GlobalCorrelation
+    import torch.nn.functional as F
+    torch.manual_seed(11)
+    B, C = 1, 32
+    mod = GlobalCorrelation(C).eval().cuda().to(dtype)
+    x = (torch.randn(2 * B, H, W, C) * 8).cuda().to(dtype)
+    with torch.inference_mode():
+        xn = mod.norm(x)
+        ref, tgt = xn.chunk(2, dim=0)
+        corr = torch.matmul(mod.q(ref).view(B, -1, C), mod.k(tgt).view(B, -1, C).transpose(-2, -1)) * mod.scale
+        want_flow, want_prob = mod(x, stereo=False)
+        blur = F.avg_pool2d(want_prob.view(2 * B, H * W, H * W), kernel_size=5, stride=1, padding=2).float()
+    flow, prob = _ma().flow_init(corr, H, W)
+    assert _close16(prob, want_prob, dtype)
+    top2 = blur.topk(2, dim=-1).values
+    clear = ((top2[..., 0] - top2[..., 1]) > (1e-6 if dtype == torch.float32 else 0.0)).view(2 * B, H, W)
+    assert clear.float().mean() > 0.5
+    assert _close16(flow[clear], want_flow[clear], dtype, ulps=2.0)
