@@ -151,6 +151,16 @@ MATCHATTN_API int matchattn_fused_forward_glue(const void *max_offset, const voi
  *                    3 = the sorting passes only, then the direct kernel walking the queries
  *                        in sorted order (the tiles are then shared through L1 instead of
  *                        shared memory; heads may look at different places).
+ *                    5 = staged tiles: every block takes a tile of 16 x QH queries, finds the extent of
+ *                        their windows and, when it fits the block's shared-memory region, has the tensor
+ *                        memory accelerator copy that K region (then the V region) in with one
+ *                        cp.async.bulk.tensor each; taps are then read from shared memory.  A tile whose
+ *                        windows spread further is served with global loads by the same block, so every
+ *                        input is accepted; it pays when neighbouring queries look at neighbouring places
+ *                        (self attention, smooth disparity / flow).  16-bit types, r = 1, head width 8 or
+ *                        16, 1/2/4/8/16 heads, at most 256 channels; MATCHATTN_ERR_VARIANT otherwise.  Needs
+ *                        no scratch; if `workspace` holds at least 8 bytes its first 8 receive the number
+ *                        of tiles that fell back to global loads (a 64-bit counter, cleared by the call).
  * Still allocates nothing and does not synchronise.  No counterpart in the reference
  * (its driver allocates its own temporaries, models/src/match_former_fused_forward.cu:492-508).
  */

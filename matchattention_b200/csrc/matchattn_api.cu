@@ -8,6 +8,7 @@
 #include "matchattn_kernels.cuh"
 #include "matchattn_mma.cuh"
 #include "matchattn_binned.cuh"
+#include "matchattn_staged.cuh"
 
 namespace matchattn {
 namespace {
@@ -21,7 +22,8 @@ struct Plan {
 };
 
 constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2, kVariantMma2 = 3;   // 3: two items per lane
-constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2, kStrategySorted = 3, kStrategySortedMma = 4;
+constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2, kStrategySorted = 3, kStrategySortedMma = 4,
+              kStrategyStaged = 5;
 constexpr long long kBinnedMinQueries = 32768;   // below this the three sorting passes cost more than they save
 
 // Geometry of the binned path; valid == false when the arguments are outside what it covers.
@@ -62,6 +64,71 @@ BinGeometry bin_geometry(int B, int H, int W, int h, int hd, int r, int dtype, i
     gmt.valid = true;
     return gmt;
 }
+// ---- staged path: geometry and tensor maps ------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime (the library does not link libcuda).
+EncodeTiledFn encode_tiled()
+{
+    static const EncodeTiledFn fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return static_cast<EncodeTiledFn>(nullptr);
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+struct StagedGeometry {
+    bool valid;
+    int ipt, rows_per_it, QH, RW, RH;
+};
+
+// Tile and region of the staged path; valid == false when the arguments are outside what it covers.
+StagedGeometry staged_geometry(int h, int hd, int r, int dtype)
+{
+    StagedGeometry g{};
+    if (dtype == MATCHATTN_F32 || r != 1 || (hd != 8 && hd != 16)) return g;
+    if (h != 1 && h != 2 && h != 4 && h != 8 && h != 16) return g;
+    const int C = h * hd;
+    if (C > 256) return g;                               // a box dimension holds at most 256 elements
+    const int qpi = kStagedThreads / h;                  // queries per iteration
+    g.rows_per_it = qpi / kStagedQW;
+    g.ipt = 8 / g.rows_per_it;
+    if (g.ipt < 1) g.ipt = 1;
+    if (g.ipt > kStagedMaxIPT) g.ipt = kStagedMaxIPT;
+    g.QH = g.ipt * g.rows_per_it;
+    const long long tokens = static_cast<long long>(kStagedRegionBytes) / (2LL * C);
+    int S = -1;
+    while ((kStagedQW + 3 + 2 * (S + 1)) * 1LL * (g.QH + 3 + 2 * (S + 1)) <= tokens && kStagedQW + 3 + 2 * (S + 1) <= 256 &&
+           g.QH + 3 + 2 * (S + 1) <= 256)
+        ++S;
+    if (S < 0) return g;
+    g.RW = kStagedQW + 3 + 2 * S;
+    g.RH = g.QH + 3 + 2 * S;
+    g.valid = true;
+    return g;
+}
+
+bool make_kv_map(CUtensorMap *map, const void *base, int dtype, int B, int H, int W, int C, int RW, int RH)
+{
+    const EncodeTiledFn enc = encode_tiled();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H),
+                                static_cast<cuuint64_t>(B)};
+    const cuuint64_t strides[3] = {2ull * C, 2ull * C * W, 2ull * C * W * H};          // bytes, dimensions 1..3
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(C), static_cast<cuuint32_t>(RW), static_cast<cuuint32_t>(RH), 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUtensorMapDataType dt = dtype == MATCHATTN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    return enc(map, dt, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 inline bool is_pow2_float(float v)
 {
     int e = 0;
@@ -301,6 +368,35 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
                        : dtype == MATCHATTN_BF16 ? __bfloat162float(__float2bfloat16_rn(hy)) : hy;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+
+    // staged path: K/V tiles copied to shared memory by the tensor memory accelerator, per tile of queries
+    if (strategy == kStrategyStaged) {
+        const StagedGeometry sg = staged_geometry(h, hd, r, dtype);
+        if (!sg.valid || !pl.fast || pl.lph != 1 || has_glue || !aligned(k, 16) || !aligned(v, 16) || H > 65535 * 8)
+            return MATCHATTN_ERR_VARIANT;
+        CUtensorMap map_k, map_v;
+        if (!make_kv_map(&map_k, k, dtype, B, H, W, static_cast<int>(C), sg.RW, sg.RH) ||
+            !make_kv_map(&map_v, v, dtype, B, H, W, static_cast<int>(C), sg.RW, sg.RH))
+            return MATCHATTN_ERR_VARIANT;
+        StagedParams sp{};
+        sp.p = p;
+        sp.ipt = sg.ipt; sp.rows_per_it = sg.rows_per_it; sp.QH = sg.QH; sp.RW = sg.RW; sp.RH = sg.RH;
+        sp.tiles_x = (W + kStagedQW - 1) / kStagedQW;
+        sp.region_bytes = static_cast<uint32_t>(2LL * C * sg.RW * sg.RH);
+        sp.fallback_tiles = nullptr;
+        if (workspace != nullptr && workspace_bytes >= 8 && aligned(workspace, 8)) {
+            sp.fallback_tiles = static_cast<unsigned long long *>(workspace);
+            cudaError_t e = cudaMemsetAsync(workspace, 0, 8, stream);
+            if (e != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(e);
+        }
+        const long long tiles = 1LL * sp.tiles_x * ((p.rows + sg.QH - 1) / sg.QH);
+        if (tiles > 2147483647LL) return MATCHATTN_ERR_TOO_LARGE;
+        const dim3 grid(static_cast<unsigned>(tiles), B);
+        const size_t smem = sp.region_bytes + 128;
+        cudaError_t err = dtype == MATCHATTN_F16 ? launch_staged<__half>(sp, pl.cpl, map_k, map_v, grid, smem, stream)
+                                                 : launch_staged<__nv_bfloat16>(sp, pl.cpl, map_k, map_v, grid, smem, stream);
+        return err == cudaSuccess ? MATCHATTN_OK : MATCHATTN_ERR_CUDA + static_cast<int>(err);
+    }
 
     // binned path: sort the queries by target tile, serve each tile from shared memory
     if (strategy != kStrategyDirect) {

@@ -4,6 +4,7 @@
 #ifdef MATCHATTN_T_IS_16BIT
 #include "matchattn_mma.cuh"
 #include "matchattn_binned.cuh"
+#include "matchattn_staged.cuh"
 #endif
 
 namespace matchattn {
@@ -106,6 +107,32 @@ cudaError_t launch_binned<MATCHATTN_T>(const BinParams &bp, int cpl, int grid_bl
     case 5: return launch_binned_cpl<MATCHATTN_T, 5>(bp, grid_blocks, smem_bytes, stream);
     default: return cudaErrorInvalidValue;
     }
+}
+#endif
+
+#ifdef MATCHATTN_T_IS_16BIT
+template <typename T, int CPL, bool POW2>
+static cudaError_t launch_staged_one(const StagedParams &sp, const CUtensorMap &map_k, const CUtensorMap &map_v, dim3 grid,
+                                     size_t smem_bytes, cudaStream_t stream)
+{
+    // per-device attribute of the kernel: set on every launch (cheap, idempotent, thread-safe)
+    cudaError_t e = cudaFuncSetAttribute(staged_forward_kernel<T, CPL, POW2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kStagedRegionBytes + 128));
+    if (e != cudaSuccess) return e;
+    staged_forward_kernel<T, CPL, POW2><<<grid, kStagedThreads, smem_bytes, stream>>>(sp, map_k, map_v);
+    return cudaGetLastError();
+}
+
+template <>
+cudaError_t launch_staged<MATCHATTN_T>(const StagedParams &sp, int cpl, const CUtensorMap &map_k, const CUtensorMap &map_v,
+                                       dim3 grid, size_t smem_bytes, cudaStream_t stream)
+{
+    const bool pow2 = sp.p.scale_pow2 != 0;
+    if (cpl == 1) return pow2 ? launch_staged_one<MATCHATTN_T, 1, true>(sp, map_k, map_v, grid, smem_bytes, stream)
+                              : launch_staged_one<MATCHATTN_T, 1, false>(sp, map_k, map_v, grid, smem_bytes, stream);
+    if (cpl == 2) return pow2 ? launch_staged_one<MATCHATTN_T, 2, true>(sp, map_k, map_v, grid, smem_bytes, stream)
+                              : launch_staged_one<MATCHATTN_T, 2, false>(sp, map_k, map_v, grid, smem_bytes, stream);
+    return cudaErrorInvalidValue;
 }
 #endif
 

@@ -67,6 +67,7 @@ def _check_tensors(max_offset, q, k, v, output, attn_out, H, W, rows, attn_num):
 
 
 STRATEGY_AUTO, STRATEGY_DIRECT, STRATEGY_BINNED = 0, 1, 2
+STRATEGY_STAGED = 5
 
 # scratch for the binned path, one buffer per (device, stream): calls on one stream are ordered, so
 # they can share it; calls on different streams may overlap on the device and must not
@@ -99,7 +100,10 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
     a row band, the query-side tensors hold rows [q_row_begin, q_row_end) only.
     ``strategy``: 0 lets the library choose (currently the direct kernel), 1 forces
     the direct kernel, 2 the binned path (queries sorted by target tile, K/V tiles
-    staged in shared memory; 16-bit types, r = 1, head width <= 40).  The binned path needs scratch
+    staged in shared memory; 16-bit types, r = 1, head width <= 40), 5 the staged path (per tile of
+    queries the K/V region its windows fall into is copied to shared memory by the tensor memory
+    accelerator; tiles whose windows spread too far use global loads; 16-bit types, r = 1, head width 8 or
+    16, at most 16 heads).  The binned path needs scratch
     memory: ``workspace`` (a uint8 CUDA tensor) or, when strategy >= 2 is asked for without one, a
     buffer this module allocates once per (device, stream) and keeps; strategy 0 and 1 allocate
     nothing.  The tuning knobs (tile_w, force_generic, chunks_per_lane, variant) belong to the
@@ -127,6 +131,11 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
         elif strategy == STRATEGY_AUTO and workspace is None:
             # the library's own choice needs no scratch: nothing is looked up or allocated here
             status = _lib.lib.matchattn_fused_forward(*args)
+        elif strategy == STRATEGY_STAGED:
+            # needs no scratch; an 8-byte workspace, if given, receives the number of tiles that were
+            # served by global loads because their windows did not fit the staged region
+            ws_ptr, ws_len = (workspace.data_ptr(), workspace.numel()) if workspace is not None else (None, 0)
+            status = _lib.lib.matchattn_fused_forward_ws(*args, ws_ptr, ws_len, int(strategy))
         else:
             need = workspace_bytes(B, H, W, h, hd, rx, q.dtype, q_row_begin, q_row_end) if rx == ry else 0
             ws_ptr, ws_len = None, 0
