@@ -133,6 +133,23 @@ MATCHATTN_API int matchattn_fused_forward_glue(const void *max_offset, const voi
                                                long long attn_row_stride, void *cuda_stream);
 
 /*
+ * The operator with every index checked on the device: the debugging aid for hosts that cannot run a
+ * memory checker.  Same arguments and results as matchattn_fused_forward (direct kernels), plus
+ *   status  16 bytes of device memory, 8-byte aligned; cleared by the call, then
+ *           [0] = number of indices (key/value taps, query-side rows) that left their array,
+ *           [1] = the first offender as block << 32 | thread << 8 | kind (1 tap, 2 query row), 0 if none.
+ * An index that fails the check is only recorded; the access itself is the clamped one of the normal
+ * kernel, so the call never faults.  Read `status` after synchronising the stream.  Runs the build of the
+ * kernel that also honours the rarely used options, which is a few per cent slower than the plain one.
+ * No counterpart in the reference (its driver checks nothing, models/src/match_former_fused_forward.cu:461-628).
+ */
+MATCHATTN_API int matchattn_fused_forward_checked(const void *max_offset, const void *q, const void *k, const void *v,
+                                                  void *out, void *attn_out,
+                                                  int B, int H, int W, int h, int hd, int rx, int ry,
+                                                  int dtype, int attn_type, float scale,
+                                                  int q_row_begin, int q_row_end, void *status, void *cuda_stream);
+
+/*
  * The same operator with scratch memory from the caller, which opens the binned
  * path: the queries are counting-sorted by the tile of the token map their window
  * falls into and each tile of K/V is staged in shared memory once for all the

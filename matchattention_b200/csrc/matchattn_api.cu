@@ -281,6 +281,7 @@ struct Glue {
     const void *gate = nullptr;
     int clamp = 0;
     long long out_stride = 0, attn_stride = 0;      // 0 = natural
+    unsigned long long *debug = nullptr;            // checked entry point: status words
 };
 
 int forward_impl(const void *max_offset, const void *q, const void *k, const void *v, void *out, void *attn_out,
@@ -308,7 +309,8 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     const long long attn_stride = glue.attn_stride > 0 ? glue.attn_stride : 1LL * h * M;
     if (out_stride < C || attn_stride < 1LL * h * M || out_stride >= (1LL << 30) || attn_stride >= (1LL << 30))
         return MATCHATTN_ERR_SHAPE;
-    const bool has_glue = glue.gate != nullptr || glue.clamp != 0 || out_stride != C || attn_stride != 1LL * h * M;
+    const bool has_glue = glue.gate != nullptr || glue.clamp != 0 || out_stride != C || attn_stride != 1LL * h * M ||
+                          glue.debug != nullptr;
     if (has_glue && (strategy == kStrategyBinned || variant == kVariantMma || variant == kVariantMma2)) return MATCHATTN_ERR_VARIANT;
     if (!aligned(glue.gate, esize)) return MATCHATTN_ERR_ALIGN;
     if (!aligned(max_offset, 2 * esize) || !aligned(q, esize) || !aligned(k, esize) || !aligned(v, esize) ||
@@ -358,6 +360,7 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     p.out_stride = static_cast<int>(out_stride);
     p.attn_stride = static_cast<int>(attn_stride);
     p.clamp = glue.clamp;
+    p.debug = glue.debug;
     if (glue.clamp) {
         // the caller's bounds (models/attention_blocks.py:49-52), rounded to the tensor type as there
         const float hx = static_cast<float>(W - 1 - r - 1e-3), hy = static_cast<float>(H - 1 - r - 1e-3);
@@ -487,6 +490,21 @@ int matchattn_fused_forward_glue(const void *max_offset, const void *q, const vo
     glue.clamp = clamp_offsets;
     glue.out_stride = out_row_stride;
     glue.attn_stride = attn_row_stride;
+    return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
+                                   scale, q_row_begin, q_row_end, cuda_stream, 0, 0, 0, 0, nullptr, 0,
+                                   matchattn::kStrategyDirect, glue);
+}
+
+int matchattn_fused_forward_checked(const void *max_offset, const void *q, const void *k, const void *v, void *out,
+                                    void *attn_out, int B, int H, int W, int h, int hd, int rx, int ry, int dtype,
+                                    int attn_type, float scale, int q_row_begin, int q_row_end, void *status,
+                                    void *cuda_stream)
+{
+    if (status == nullptr || (reinterpret_cast<uintptr_t>(status) & 7)) return MATCHATTN_ERR_NULL;
+    cudaError_t e = cudaMemsetAsync(status, 0, 16, static_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(e);
+    matchattn::Glue glue;
+    glue.debug = static_cast<unsigned long long *>(status);
     return matchattn::forward_impl(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, rx, ry, dtype, attn_type,
                                    scale, q_row_begin, q_row_end, cuda_stream, 0, 0, 0, 0, nullptr, 0,
                                    matchattn::kStrategyDirect, glue);

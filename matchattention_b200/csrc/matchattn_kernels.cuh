@@ -57,7 +57,16 @@ struct Params {
     int clamp;               // non-zero: clamp the centre to [lo, hi_x] x [lo, hi_y] first, as the caller would
     float clamp_lo, clamp_hi_x, clamp_hi_y;   // bounds, already rounded to T
     int scale_pow2;          // non-zero: 16-bit type and `scale` is a power of two that the type represents exactly
+    unsigned long long *debug;   // when not null (checked entry point): [0] counts out-of-range indices, [1] keeps the first
 };
+
+// Records an index that left its array (checked entry point only): a count and the first offender as
+// (block << 32 | thread << 8 | what), what = 1 key/value tap, 2 query-side row.
+__device__ __forceinline__ void debug_record(unsigned long long *dbg, unsigned what)
+{
+    atomicAdd(&dbg[0], 1ull);
+    atomicCAS(&dbg[1], 0ull, (static_cast<unsigned long long>(blockIdx.x) << 32) | (threadIdx.x << 8) | what);
+}
 
 // torch.clamp semantics: NaN stays NaN
 __device__ __forceinline__ float clamp_keep_nan(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
@@ -576,6 +585,20 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     const T *kb = static_cast<const T *>(p.k) + kv_base;
     const T *vb = static_cast<const T *>(p.v) + kv_base;
 
+    if (EXTRAS && p.debug != nullptr) {
+        // checked entry point: every index this lane is about to use, against the extent of its array
+        const int64_t item_elems = static_cast<int64_t>(p.N) * p.C;
+#pragma unroll
+        for (int j = 0; j < SIDE; ++j)
+#pragma unroll
+            for (int i = 0; i < SIDE; ++i) {
+                const int64_t first = static_cast<int64_t>(row[j]) + col[i] / static_cast<uint32_t>(sizeof(T)) + lane_off;
+                if (row[j] < 0 || first < 0 || first + SLICE > item_elems) debug_record(p.debug, 1u);
+            }
+        if (bq < 0 || bq >= static_cast<int64_t>(p.B) * p.Nq || lane_off + SLICE > p.C || b < 0 || b >= p.B)
+            debug_record(p.debug, 2u);
+    }
+
     uint32_t qw[NW];
     load_words<NW>(qw, static_cast<const T *>(p.q) + bq * p.C + lane_off);
 
@@ -725,6 +748,7 @@ __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params 
         const int ty = min(max(y0 + j, 0), p.H - 1);
         for (int i = 0; i < side; ++i) {
             const int tx = min(max(x0 + i, 0), p.W - 1);
+            if (p.debug != nullptr && (ty < 0 || ty >= p.H || tx < 0 || tx >= p.W)) debug_record(p.debug, 1u);
             const T *kp = kb + static_cast<int64_t>(ty * p.W + tx) * p.C;
             float acc = 0.f;
             for (int c = 0; c < p.hd; ++c) acc += fabsf(DT<T>::rnd(load_one<T>(qp + c) - load_one<T>(kp + c)));

@@ -23,7 +23,13 @@ from typing import List, Optional, Tuple
 import torch
 import torch.nn as nn
 
+import os
+
 from . import _lib
+
+# MATCHATTN_B200_NVTX=1 wraps every operator launch in an NVTX range named after its shape, so that a
+# profiler's NVTX filter can pick the operator out of a model's timeline (off by default: two extra calls)
+_NVTX = os.environ.get("MATCHATTN_B200_NVTX", "0") not in ("", "0")
 
 _DTYPE_CODE = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 
@@ -119,6 +125,8 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
     knobs = tile_w or force_generic or chunks_per_lane or variant
     if knobs and strategy == STRATEGY_BINNED:
         raise ValueError("the direct-kernel knobs cannot be combined with strategy=2")
+    if _NVTX:
+        torch.cuda.nvtx.range_push(f"matchattn_b200 B{B} {H}x{W} h{h}x{hd} r{rx} {str(q.dtype)[6:]}")
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
         args = (max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
@@ -146,7 +154,25 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
                     raise ValueError("workspace must be a contiguous uint8 tensor on q's device")
                 ws_ptr, ws_len = workspace.data_ptr(), workspace.numel()
             status = _lib.lib.matchattn_fused_forward_ws(*args, ws_ptr, ws_len, int(strategy))
+    if _NVTX:
+        torch.cuda.nvtx.range_pop()
     _lib.check(status)
+
+
+def launch_checked(max_offset, q, k, v, output, attn_out, H: int, W: int, r: int, scale: float):
+    """The operator through matchattn_fused_forward_checked: every index is checked on the device.
+    Returns (violations, first_offender) after synchronising; both 0 for a healthy kernel."""
+    attn_num = (2 * r + 2) ** 2
+    B, h, hd = _check_tensors(max_offset, q, k, v, output, attn_out, H, W, H, attn_num)
+    status_words = torch.empty(2, dtype=torch.int64, device=q.device)
+    with torch.cuda.device(q.device):
+        status = _lib.lib.matchattn_fused_forward_checked(
+            max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
+            attn_out.data_ptr() if attn_out is not None else None, B, H, W, h, hd, r, r, _DTYPE_CODE[q.dtype],
+            _lib.L1_NORM, float(scale), 0, H, status_words.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    _lib.check(status)
+    words = status_words.cpu()
+    return int(words[0]), int(words[1])
 
 
 def fused_forward(max_offset, q, k, v, output, attn_out, H, W, win_r, attn_num, attn_type, scale) -> None:

@@ -101,3 +101,24 @@ def test_bad_arguments_raise_and_leave_the_device_usable(case):
     out, _ = match_attention(mo, q, k, v, H, W, 1, 0.25)
     torch.cuda.synchronize()
     assert_close(out, case["ref"][0], torch.float16)
+
+
+def test_checked_entry_point_finds_no_stray_index():
+    """matchattn_fused_forward_checked: the same results as the plain call, and not one index outside its
+    array, on the inputs most likely to produce one: centres far outside the map, NaN, infinities, the
+    smallest map that fits the window, odd sizes, the any-shape kernel."""
+    import matchattention_b200 as ma
+    from _cases import make_inputs
+    for B, H, W, h, hd, r, dtype in ((2, 33, 29, 8, 16, 1, torch.float16), (1, 4, 4, 2, 16, 1, torch.float32),
+                                     (1, 17, 19, 4, 40, 2, torch.bfloat16), (1, 12, 14, 5, 12, 1, torch.float16)):
+        mo, q, k, v = (t.cuda() for t in make_inputs(91, B, H, W, h, hd, r, dtype, kind="raw"))
+        mo[0, 0, 0, 0] = float("nan")
+        mo[0, 1, 0, 1] = float("inf")
+        mo[0, 2, :, :] = -60000.0
+        out, attn = torch.empty_like(q), q.new_empty(B, H * W, h, (2 * r + 2) ** 2)
+        violations, first = ma.ops.launch_checked(mo, q, k, v, out, attn, H, W, r, hd ** -0.5)
+        assert (violations, first) == (0, 0)
+        want_out, want_attn = ma.match_attention(mo, q, k, v, H, W, r, hd ** -0.5)
+        torch.cuda.synchronize()
+        same = lambda a, b: torch.equal(torch.nan_to_num(a.float(), nan=7.0), torch.nan_to_num(b.float(), nan=7.0))
+        assert same(out, want_out) and same(attn, want_attn)
