@@ -150,6 +150,27 @@ MATCHATTN_API int matchattn_fused_forward_checked(const void *max_offset, const 
                                                   int q_row_begin, int q_row_end, void *status, void *cuda_stream);
 
 /*
+ * Backward of the operator: gradients with respect to q, k, v and max_offset, given the gradients of both
+ * outputs.  The reference's native path has none (models/match_former_ops.py registers no autograd; the
+ * attn_sum buffer "for backward" of models/src/match_former_fused_forward.cu:409,495 is never read); what is
+ * computed is what autograd computes over the reference's 'pytorch' path (models/mat_pytorch_impl.py:3-178
+ * driven by models/attention_blocks.py:82-91).
+ *   d_out        [B, Nq, h*hd]            gradient of out
+ *   d_attn       [B, Nq, h, (2r+2)^2]     gradient of attn_out, or NULL (the self branch discards attn_out)
+ *   d_q          [B, Nq, h*hd]            written (tensor type)
+ *   d_k, d_v     [B, H*W, h*hd] float32   ACCUMULATED with atomic adds: the caller zeroes them (or passes running sums)
+ *   d_max_offset [B, Nq, h, 2]            written, or NULL: through the bilinear weights (floor has no gradient)
+ * Nothing is saved by the forward; the kernel recomputes what it needs, in float32 whatever the tensor type.
+ * Allocates nothing, launches on `cuda_stream`.
+ */
+MATCHATTN_API int matchattn_fused_backward(const void *max_offset, const void *q, const void *k, const void *v,
+                                           const void *d_out, const void *d_attn,
+                                           void *d_q, float *d_k, float *d_v, void *d_max_offset,
+                                           int B, int H, int W, int h, int hd, int rx, int ry,
+                                           int dtype, int attn_type, float scale,
+                                           int q_row_begin, int q_row_end, void *cuda_stream);
+
+/*
  * The same operator with scratch memory from the caller, which opens the binned
  * path: the queries are counting-sorted by the tile of the token map their window
  * falls into and each tile of K/V is staged in shared memory once for all the

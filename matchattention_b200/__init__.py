@@ -20,7 +20,7 @@ import importlib
 
 _OPS = ("MF_FusedForwardOps", "describe_dispatch", "fused_forward", "fused_forward_ops", "launch",
         "match_attention", "workspace_bytes", "cross_attention_core", "self_attention_core", "launch_glue",
-        "upsample_field", "stereo_volume", "consistency_mask", "local_disparity_estimator", "flow_init")
+        "upsample_field", "stereo_volume", "consistency_mask", "local_disparity_estimator", "flow_init", "match_attention_autograd")
 __all__ = list(_OPS) + ["install_dropin", "abi_version"]
 
 

@@ -13,7 +13,8 @@ LIB_PATH = os.path.join(_PKG, "lib", "libmatchattn_b200.so")
 
 # every symbol include/matchattn.h declares
 EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_fused_forward_ws",
-           "matchattn_fused_forward_static", "matchattn_fused_forward_glue", "matchattn_fused_forward_checked", "matchattn_upsample_field",
+           "matchattn_fused_forward_static", "matchattn_fused_forward_glue", "matchattn_fused_forward_checked",
+           "matchattn_fused_backward", "matchattn_upsample_field",
            "matchattn_stereo_volume", "matchattn_consistency_mask", "matchattn_local_disparity",
            "matchattn_flow_init", "matchattn_flow_init_scratch_bytes",
            "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
@@ -41,6 +42,8 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_fused_forward_static.argtypes = base
     lib.matchattn_fused_forward_checked.restype = _i
     lib.matchattn_fused_forward_checked.argtypes = [_vp] * 6 + [_i] * 9 + [_f, _i, _i, _vp, _vp]
+    lib.matchattn_fused_backward.restype = _i
+    lib.matchattn_fused_backward.argtypes = [_vp] * 10 + [_i] * 9 + [_f, _i, _i, _vp]
     lib.matchattn_fused_forward_glue.restype = _i
     lib.matchattn_fused_forward_glue.argtypes = [_vp] * 7 + [_i] * 9 + [_f, _i, _i, _i, ctypes.c_longlong,
                                                  ctypes.c_longlong, _vp]

@@ -23,7 +23,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libmatchattn_b200.so")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 
 SOURCES = ["matchattn_api.cu", "matchattn_f32.cu", "matchattn_f16.cu", "matchattn_bf16.cu",
-           "matchattn_static_scratch.cu", "matchattn_upsample.cu", "matchattn_volume.cu", "matchattn_field_ops.cu", "matchattn_flow_init.cu"]
+           "matchattn_static_scratch.cu", "matchattn_upsample.cu", "matchattn_volume.cu", "matchattn_field_ops.cu", "matchattn_flow_init.cu", "matchattn_backward.cu"]
 HEADERS = ["matchattn_kernels.cuh", "matchattn_launch.inl", "matchattn_mma.cuh", "matchattn_binned.cuh",
            "matchattn_staged.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,0 +1,176 @@
+// Backward of the MatchAttention operator.
+//
+// The reference's native path has no backward (models/match_former_ops.py registers none; the attn_sum
+// buffer "for backward" of models/src/match_former_fused_forward.cu:409,495 is never read); only its 'pytorch'
+// path can be trained, through autograd over the five functions of models/mat_pytorch_impl.py.  This kernel
+// computes what that autograd computes: gradients with respect to q, k, v and max_offset, given the
+// gradients of both outputs (out and attn_out: the cross branch feeds the attention weights to its output
+// projection, models/attention_blocks.py:95-98).
+//
+//   s_m   = -scale * sum_c |q_c - k_mc|                         scores of the (2r+2)^2 taps
+//   p_t   = softmax of s over sub-window t (t = nw, ne, sw, se)  a_m = sum_t w_t p_tm,  out_c = sum_m a_m v_mc
+//   da_m  = sum_c dout_c v_mc + dattn_m                          dv_mc += a_m dout_c
+//   ds_m  = sum_t w_t p_tm (da_m - sum_m' p_tm' da_m')           dw_t   = sum_m p_tm da_m
+//   dq_c  = -scale sum_m ds_m sign(q_c - k_mc)                   dk_mc += scale ds_m sign(q_c - k_mc)
+//   d(max_offset) follows from dw through w = [(1-dx)(1-dy), dx(1-dy), (1-dx)dy, dx dy] (floor has no gradient)
+//
+// One thread per (query, head); the forward quantities are recomputed (nothing is saved by the forward);
+// all arithmetic in float32 whatever the tensor type; dk and dv are float32 arrays [B, H*W, C] that the
+// caller has zeroed, filled with atomic adds (several queries look at the same token).  Correct and tested
+// against autograd; not tuned (the reference offers no faster backward to compare with).
+#include "../../include/matchattn.h"
+
+#include <stdint.h>
+
+#include "matchattn_kernels.cuh"
+
+namespace matchattn {
+namespace {
+
+struct BwdParams {
+    const void *mo, *q, *k, *v, *dout, *dattn;   // dattn may be null
+    void *dq, *dmo;                               // tensor type; dmo may be null
+    float *dk, *dv;                               // float32, pre-zeroed
+    int B, H, W, h, hd, C, r, rows, Nq, N;
+    float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) backward_kernel(const BwdParams p)
+{
+    const int64_t per_item = static_cast<int64_t>(p.Nq) * p.h;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= per_item) return;
+    const int b = blockIdx.y;
+    const int head = static_cast<int>(t % p.h);
+    const int64_t bq = static_cast<int64_t>(b) * p.Nq + t / p.h;
+    const int r = p.r, side = 2 * r + 2, sub = 2 * r + 1, M = side * side;
+
+    const T *mo = static_cast<const T *>(p.mo) + (bq * p.h + head) * 2;
+    const float x = load_one<T>(mo), y = load_one<T>(mo + 1);
+    const float xf = floorf(x), yf = floorf(y);
+    const float dx = x - xf, dy = y - yf;
+    const float wgt[4] = {(1.f - dx) * (1.f - dy), dx * (1.f - dy), (1.f - dx) * dy, dx * dy};
+    const int x0 = window_origin(xf, r, p.W) - r, y0 = window_origin(yf, r, p.H) - r;
+
+    const int64_t qoff = bq * p.C + head * p.hd;
+    const T *qp = static_cast<const T *>(p.q) + qoff;
+    const T *gop = static_cast<const T *>(p.dout) + qoff;
+    const int64_t kv_base = static_cast<int64_t>(b) * p.N * p.C + head * p.hd;
+    const T *kb = static_cast<const T *>(p.k) + kv_base;
+    const T *vb = static_cast<const T *>(p.v) + kv_base;
+
+    // forward: scores, sub-window softmaxes, attention weights; da from dout.v (+ dattn)
+    float s[kMaxTaps], a[kMaxTaps], da[kMaxTaps];
+    int tok[kMaxTaps];
+    for (int j = 0; j < side; ++j) {
+        const int ty = min(max(y0 + j, 0), p.H - 1);
+        for (int i = 0; i < side; ++i) {
+            const int tx = min(max(x0 + i, 0), p.W - 1);
+            const int m = j * side + i;
+            tok[m] = ty * p.W + tx;
+            const T *kp = kb + static_cast<int64_t>(tok[m]) * p.C;
+            const T *vp = vb + static_cast<int64_t>(tok[m]) * p.C;
+            float l1 = 0.f, dot = 0.f;
+            for (int c = 0; c < p.hd; ++c) {
+                l1 += fabsf(load_one<T>(qp + c) - load_one<T>(kp + c));
+                dot = fmaf(load_one<T>(gop + c), load_one<T>(vp + c), dot);
+            }
+            s[m] = -l1 * p.scale;
+            a[m] = 0.f;
+            da[m] = dot;
+        }
+    }
+    if (p.dattn != nullptr) {
+        const T *gap = static_cast<const T *>(p.dattn) + (bq * p.h + head) * M;
+        for (int m = 0; m < M; ++m) da[m] += load_one<T>(gap + m);
+    }
+    float ds[kMaxTaps], dw[4];
+    for (int m = 0; m < M; ++m) ds[m] = 0.f;
+    for (int tq = 0; tq < 4; ++tq) {
+        const int oy = tq >> 1, ox = tq & 1;
+        float mx = -INFINITY;
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) mx = fmaxf(mx, s[(j + oy) * side + i + ox]);
+        float den = 0.f;
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) den += expf(s[(j + oy) * side + i + ox] - mx);
+        const float inv = 1.f / den;
+        float pda = 0.f;                                   // sum_m p_tm da_m
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) {
+                const int m = (j + oy) * side + i + ox;
+                const float pr = expf(s[m] - mx) * inv;
+                a[m] += wgt[tq] * pr;
+                pda = fmaf(pr, da[m], pda);
+            }
+        dw[tq] = pda;
+        for (int j = 0; j < sub; ++j)
+            for (int i = 0; i < sub; ++i) {
+                const int m = (j + oy) * side + i + ox;
+                const float pr = expf(s[m] - mx) * inv;
+                ds[m] = fmaf(wgt[tq] * pr, da[m] - pda, ds[m]);
+            }
+    }
+
+    // gradient of the sampling centre through the bilinear weights
+    if (p.dmo != nullptr) {
+        T *gmo = static_cast<T *>(p.dmo) + (bq * p.h + head) * 2;
+        store_one<T>(gmo, (1.f - dy) * (dw[1] - dw[0]) + dy * (dw[3] - dw[2]));
+        store_one<T>(gmo + 1, (1.f - dx) * (dw[2] - dw[0]) + dx * (dw[3] - dw[1]));
+    }
+
+    // dq, and the scatter into dk / dv
+    T *gq = static_cast<T *>(p.dq) + qoff;
+    for (int c = 0; c < p.hd; ++c) {
+        const float qc = load_one<T>(qp + c), go = load_one<T>(gop + c);
+        float acc = 0.f;
+        for (int m = 0; m < M; ++m) {
+            const int64_t off = static_cast<int64_t>(tok[m]) * p.C + c;
+            const float d = qc - load_one<T>(kb + off);
+            const float sg = d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f);
+            const float g = p.scale * ds[m] * sg;
+            acc -= g;
+            if (g != 0.f) atomicAdd(p.dk + kv_base + off, g);
+            const float gv = a[m] * go;
+            if (gv != 0.f) atomicAdd(p.dv + kv_base + off, gv);
+        }
+        store_one<T>(gq + c, acc);
+    }
+}
+
+}  // namespace
+}  // namespace matchattn
+
+extern "C" int matchattn_fused_backward(const void *max_offset, const void *q, const void *k, const void *v,
+                                        const void *d_out, const void *d_attn, void *d_q, float *d_k, float *d_v,
+                                        void *d_max_offset, int B, int H, int W, int h, int hd, int rx, int ry, int dtype,
+                                        int attn_type, float scale, int q_row_begin, int q_row_end, void *cuda_stream)
+{
+    using namespace matchattn;
+    if (!max_offset || !q || !k || !v || !d_out || !d_q || !d_k || !d_v) return MATCHATTN_ERR_NULL;
+    if (dtype != MATCHATTN_F32 && dtype != MATCHATTN_F16 && dtype != MATCHATTN_BF16) return MATCHATTN_ERR_DTYPE;
+    if (attn_type != MATCHATTN_L1_NORM) return MATCHATTN_ERR_ATTN_TYPE;
+    if (B <= 0 || H <= 0 || W <= 0 || h <= 0 || hd <= 0) return MATCHATTN_ERR_SHAPE;
+    if (q_row_begin < 0 || q_row_end > H || q_row_begin >= q_row_end) return MATCHATTN_ERR_SHAPE;
+    if (rx != ry || rx < 0 || rx > MATCHATTN_MAX_R) return MATCHATTN_ERR_WINDOW;
+    if (2 * rx + 2 > W || 2 * ry + 2 > H) return MATCHATTN_ERR_WINDOW_FIT;
+    const long long C = 1LL * h * hd, N = 1LL * H * W, Nq = 1LL * (q_row_end - q_row_begin) * W;
+    if (C > 65536 || N * C >= 2147483647LL || Nq * h >= 2147483647LL || B > 65535) return MATCHATTN_ERR_TOO_LARGE;
+    BwdParams p{};
+    p.mo = max_offset; p.q = q; p.k = k; p.v = v; p.dout = d_out; p.dattn = d_attn;
+    p.dq = d_q; p.dmo = d_max_offset; p.dk = d_k; p.dv = d_v;
+    p.B = B; p.H = H; p.W = W; p.h = h; p.hd = hd; p.C = static_cast<int>(C); p.r = rx;
+    p.rows = q_row_end - q_row_begin; p.Nq = static_cast<int>(Nq); p.N = static_cast<int>(N);
+    p.scale = scale;
+    const long long per_item = Nq * h;
+    const dim3 grid(static_cast<unsigned>((per_item + 127) / 128), B);
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    switch (dtype) {
+    case MATCHATTN_F32: backward_kernel<float><<<grid, 128, 0, stream>>>(p); break;
+    case MATCHATTN_F16: backward_kernel<__half><<<grid, 128, 0, stream>>>(p); break;
+    default: backward_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(p); break;
+    }
+    const cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? MATCHATTN_OK : MATCHATTN_ERR_CUDA + static_cast<int>(err);
+}

@@ -206,11 +206,17 @@ def _(max_offset, q, k, v, output, attn_out, H, W, win_r, attn_num, attn_type, s
 class MF_FusedForwardOps(nn.Module):
     """Same call and return values as the reference module of this name
     (models/match_former_ops.py:65-121); outputs are allocated uninitialised
-    because the kernel overwrites every element."""
+    because the kernel overwrites every element.  Unlike the reference's module it can be trained through:
+    when an input requires a gradient the call goes through match_attention_autograd."""
 
     def forward(self, max_offset: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, H: int, W: int,
                 win_r: List[int], attn_num: int, attn_type: str = "l1_norm",
                 scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+        if torch.is_grad_enabled() and any(t.requires_grad for t in (max_offset, q, k, v)):
+            rx, ry = _window_radius(win_r)
+            if attn_type != "l1_norm" or rx != ry:
+                raise NotImplementedError("training needs attn_type 'l1_norm' and a square window")
+            return match_attention_autograd(max_offset, q, k, v, int(H), int(W), rx, scale)
         B, N, _ = q.shape
         h = max_offset.size(2)
         output = torch.empty_like(v)
@@ -236,6 +242,50 @@ def match_attention(max_offset, q, k, v, H: int, W: int, r: int, scale: float, *
 def describe_dispatch(h: int, hd: int, r: int, dtype: torch.dtype, aligned32: bool = True) -> Optional[str]:
     res = _lib.lib.matchattn_describe_dispatch(h, hd, r, _DTYPE_CODE[dtype], int(aligned32))
     return res.decode() if res is not None else None
+
+
+# ---- training: the operator as an autograd function ------------------------------------------------
+
+class _MatchAttentionFn(torch.autograd.Function):
+    """Forward = the fused kernel; backward = matchattn_fused_backward.  Nothing but the inputs is saved:
+    the backward kernel recomputes scores and softmaxes."""
+
+    @staticmethod
+    def forward(ctx, max_offset, q, k, v, H, W, r, scale):
+        out = torch.empty_like(q)
+        attn = q.new_empty(q.size(0), q.size(1), max_offset.size(2), (2 * r + 2) ** 2)
+        launch(max_offset, q, k, v, out, attn, H, W, (r, r), "l1_norm", scale)
+        ctx.save_for_backward(max_offset, q, k, v)
+        ctx.geometry = (H, W, r, scale)
+        return out, attn
+
+    @staticmethod
+    def backward(ctx, d_out, d_attn):
+        max_offset, q, k, v = ctx.saved_tensors
+        H, W, r, scale = ctx.geometry
+        B, Nq, C = q.shape
+        h = max_offset.size(2)
+        d_q = torch.empty_like(q)
+        d_mo = torch.empty_like(max_offset) if ctx.needs_input_grad[0] else None
+        d_k = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
+        d_v = torch.zeros(v.shape, dtype=torch.float32, device=v.device)
+        d_out = d_out.contiguous()
+        d_attn = d_attn.contiguous() if d_attn is not None else None
+        with torch.cuda.device(q.device):
+            status = _lib.lib.matchattn_fused_backward(
+                max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), d_out.data_ptr(),
+                d_attn.data_ptr() if d_attn is not None else None, d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(),
+                d_mo.data_ptr() if d_mo is not None else None, B, H, W, h, C // h, r, r, _DTYPE_CODE[q.dtype],
+                _lib.L1_NORM, float(scale), 0, H, torch.cuda.current_stream().cuda_stream)
+        _lib.check(status)
+        return d_mo, d_q, d_k.to(k.dtype), d_v.to(v.dtype), None, None, None, None
+
+
+def match_attention_autograd(max_offset, q, k, v, H: int, W: int, r: int, scale: float):
+    """The operator for training: (out, attn) with gradients to q, k, v and max_offset, as autograd gives them
+    for the reference's 'pytorch' path (its native path has no backward).  Contiguous CUDA tensors."""
+    return _MatchAttentionFn.apply(max_offset.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), H, W, r,
+                                   float(scale))
 
 
 # ---- the caller's glue folded into the kernel ------------------------------------------------

@@ -312,6 +312,30 @@ def flow_init_cases(ref_root):
             print(f"{name}_{tags[dtype]}: {os.path.getsize(path) / 1024:.0f} KiB")
 
 
+def backward_cases(impl):
+    """Gradients that autograd gives for the reference's 'pytorch' path (float32, CPU): of
+    sum(out * g_out) + sum(attn * g_attn) with seeded g_out, g_attn, with respect to q, k, v and max_offset."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    from _cases import make_inputs
+    for name, seed, B, H, W, h, hd, r, kind in (("backward_r1", 101, 1, 9, 11, 2, 8, 1, "flow"),
+                                                ("backward_r2", 102, 2, 7, 8, 3, 16, 2, "self")):
+        mo, q, k, v = make_inputs(seed, B, H, W, h, hd, r, torch.float32, kind=kind, spread=3.0, border_frac=0.2,
+                                  per_head=True)
+        gen = torch.Generator().manual_seed(seed + 1)
+        g_out = torch.randn(q.shape, generator=gen)
+        g_attn = torch.randn(B, H * W, h, (2 * r + 2) ** 2, generator=gen)
+        leaves = [t.clone().requires_grad_(True) for t in (mo, q, k, v)]
+        out, attn = reference_op(impl, *leaves, H, W, h, r, hd ** -0.5)
+        ((out * g_out).sum() + (attn * g_attn).sum()).backward()
+        path = os.path.join(HERE, name + "_f32.npz")
+        np.savez_compressed(path, dtype="float32", H=H, W=W, h=h, r=r, scale=np.float64(hd ** -0.5),
+                            max_offset=mo.numpy(), q=q.numpy(), k=k.numpy(), v=v.numpy(), g_out=g_out.numpy(),
+                            g_attn=g_attn.numpy(), d_max_offset=leaves[0].grad.numpy(), d_q=leaves[1].grad.numpy(),
+                            d_k=leaves[2].grad.numpy(), d_v=leaves[3].grad.numpy(),
+                            note=f"seed {seed}, autograd over the reference's mat_pytorch_impl on CPU")
+        print(f"{name}_f32: {os.path.getsize(path) / 1024:.0f} KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF"), required="MATCHATTN_REF" not in os.environ,
@@ -326,6 +350,7 @@ def main():
     if a.only_field_ops:
         field_op_cases(a.ref, blocks)
         flow_init_cases(a.ref)
+        backward_cases(impl)
         return
     if a.only_new:
         wide_head_cases(impl, blocks)
@@ -341,6 +366,7 @@ def main():
     volume_cases(a.ref)
     field_op_cases(a.ref, blocks)
     flow_init_cases(a.ref)
+    backward_cases(impl)
 
 
 if __name__ == "__main__":
