@@ -459,7 +459,7 @@ def run_model_ops_mode(args):
     print(json.dumps(line), flush=True)
 
 
-def run_model_mode(args):
+def measure_model(args, compile_ours, compile_reference, steps=None):
     """The reference's own MatchStereo forward on the GPU with its operator swapped (BASELINE.json configs[2]:
     MatchStereo-T, random-init weights, float16, a 1536x1536 synthetic stereo pair; ms per pair).
 
@@ -479,9 +479,8 @@ def run_model_mode(args):
     from oracle import ref_loader
     metric = f"matchstereo_{args.model_variant}_{args.model_size[0]}x{args.model_size[1]}_ms_per_pair"
     if not ref_loader.available():
-        print(json.dumps({"metric": metric, "unavailable": "the reference's Python code is not present under "
-                          "oracle/_ref/ (oracle/make_ref.py places it where a checkout exists)"}), flush=True)
-        return
+        return {"metric": metric, "unavailable": "the reference's Python code is not present under "
+                "oracle/_ref/ (oracle/make_ref.py places it where a checkout exists)"}
     import matchattention_b200 as ma
     from matchattention_b200.dropin.fused_model import patch_reference_model
     from _cases import make_stereo_pair
@@ -503,8 +502,8 @@ def run_model_mode(args):
         m = MatchStereo(types.SimpleNamespace(variant=args.model_variant, mat_impl=mat_impl))
         return m.eval().to(dev).to(dtype)
 
-    n = max(5, min(args.steps, 50))
-    warm = max(5, args.warmup)
+    n = max(5, min(steps if steps is not None else args.steps, 50))
+    warm = max(5, min(args.warmup, 10))
 
     def timed(fn):
         for _ in range(warm):
@@ -586,7 +585,9 @@ def run_model_mode(args):
             notes["fused_graph"] = "not captured: " + str(exc).splitlines()[0][:200]
             torch.cuda.synchronize()
         compiled_field = None
-        if args.model_compile:
+        if compile_ours or compile_reference:
+            torch.backends.cuda.matmul.allow_tf32 = True
+        if compile_ours:
             # torch.compile around the opaque ops, as the reference's own driver compiles its model
             # (run_img.py:55-58: default mode, dynamic=False, TF32 matmuls allowed)
             torch.backends.cuda.matmul.allow_tf32 = True
@@ -615,6 +616,7 @@ def run_model_mode(args):
                     torch.cuda.synchronize()
             except Exception as exc:
                 notes["fused_compiled"] = "failed: " + str(exc).splitlines()[0][:300]
+        if compile_reference:
             try:
                 del model
                 torch.cuda.empty_cache()
@@ -646,7 +648,11 @@ def run_model_mode(args):
                        "target_ms": 5.0},
             "clocks": sampler.summary(t_wall0, time.perf_counter()),
             "gpu_launches": n_calls * n}
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def run_model_mode(args):
+    print(json.dumps(measure_model(args, args.model_compile, args.model_compile)), flush=True)
 
 
 def run_upsample_mode(args):
@@ -775,6 +781,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-shapes", action="store_true", help="skip the timing of the other configuration shapes")
+    ap.add_argument("--no-model", action="store_true", help="skip the MatchStereo-T forward leg of the default line")
     ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
@@ -982,6 +989,20 @@ def main():
     if rank == 0 and not args.no_shapes and args.workload == DEFAULT_WORKLOAD:
         peak_gbs, _ = measured_peak()
         shapes = [time_shape(name, dev, peak_gbs) for name in SHAPE_WORKLOADS]
+    model = None
+    if world == 1 and not args.no_model and args.workload == DEFAULT_WORKLOAD:
+        # the other half of the metric: the reference's MatchStereo-T forward at 1536x1536 with the operator
+        # swapped, ms per pair (see measure_model; the reference's own compiled arm only with --model-compile)
+        try:
+            full = measure_model(args, compile_ours=True, compile_reference=args.model_compile, steps=10)
+            cfg = full.get("config", {})
+            model = {"metric": full["metric"], "unit": "ms", "value": full.get("value"),
+                     "arm_reported": cfg.get("arm_reported"), "arms_ms_per_pair": cfg.get("arms_ms_per_pair"),
+                     "notes": cfg.get("notes"), "field_up_rel_diff": cfg.get("field_up_rel_diff_vs_pytorch_branch"),
+                     "operator_calls_alone_graph_ms": cfg.get("operator_calls_alone_graph_ms"),
+                     "target_ms": 5.0, "workload": cfg.get("workload"), "unavailable": full.get("unavailable")}
+        except Exception as exc:
+            model = {"error": str(exc).splitlines()[0][:300] if str(exc) else type(exc).__name__}
     if sampler:
         sampler.stop()
 
@@ -1009,6 +1030,8 @@ def main():
         }
         if band is not None:
             line["band"] = band          # one huge pair split by query row bands over the same GPUs (strong scaling)
+        if model is not None:
+            line["model"] = model        # MatchStereo-T ms per pair: the reference's model around this library's kernels
         if shapes is not None:
             line["shapes"] = shapes      # the other configuration shapes, same run, same clock record
         if e2e is not None:

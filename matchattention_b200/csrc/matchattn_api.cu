@@ -24,7 +24,6 @@ struct Plan {
 constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2, kVariantMma2 = 3;   // 3: two items per lane
 constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2, kStrategySorted = 3, kStrategySortedMma = 4,
               kStrategyStaged = 5;
-constexpr long long kBinnedMinQueries = 32768;   // below this the three sorting passes cost more than they save
 
 // Geometry of the binned path; valid == false when the arguments are outside what it covers.
 struct BinGeometry {
@@ -409,10 +408,8 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
                             aligned(q, 16) && aligned(k, 16) && aligned(v, 16) && aligned(out, 16) &&
                             aligned(attn_out, 32) && aligned(max_offset, 4);
         if (strategy >= kStrategyBinned && !usable) return MATCHATTN_ERR_VARIANT;
-        // The sorting passes and the one-block-per-tile staging do not yet beat the direct kernel on
-        // the shapes measured so far, so the automatic choice stays with the direct kernel and the
-        // binned path runs on request.
-        (void)kBinnedMinQueries;
+        // The sorting passes and the staging do not beat the direct kernel on any shape measured, so the
+        // automatic choice (strategy 0) is the direct kernel and the binned path runs on request only.
         if (usable && strategy >= kStrategyBinned) {
             char *ws = static_cast<char *>(workspace);
             BinParams bp{};

@@ -152,6 +152,29 @@ __device__ __forceinline__ float add_f32_bf16(float acc, unsigned short h)
     return acc;
 }
 
+// packed float32 arithmetic of sm_100: two lanes of a 64-bit register per instruction
+__device__ __forceinline__ void fma_f32x2(float &d0, float &d1, float a, float b0, float b1)
+{
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\t"
+        "mov.b64 ra, {%2, %2};\n\t"
+        "mov.b64 rb, {%3, %4};\n\t"
+        "mov.b64 rc, {%0, %1};\n\t"
+        "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rc;\n\t}"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void sub_f32x2(float &d0, float &d1, float a0, float a1, float b0, float b1)
+{
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "sub.rn.f32x2 rc, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rc;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
 // ------------------------------------------------------------------ per-dtype arithmetic
 
 template <typename T>
@@ -616,10 +639,19 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
             uint32_t kw[NW];
             load_words<NW>(kw, tap_ptr(kb + row[j], col[i]));
             float a0 = 0.f, a1 = 0.f;
+            if constexpr (EPW == 1) {
+                // float32: two channels per packed subtract (same roundings as the scalar form)
 #pragma unroll
-            for (int w = 0; w < NW; ++w) {
-                if (EPW == 1 && (w & 1)) DT<T>::absdiff(a1, a0, qw[w], kw[w]);
-                else DT<T>::absdiff(a0, a1, qw[w], kw[w]);
+                for (int w = 0; w < NW; w += 2) {
+                    float d0, d1;
+                    sub_f32x2(d0, d1, __uint_as_float(qw[w]), __uint_as_float(qw[w + 1]), __uint_as_float(kw[w]),
+                              __uint_as_float(kw[w + 1]));
+                    a0 += fabsf(d0);
+                    a1 += fabsf(d1);
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < NW; ++w) DT<T>::absdiff(a0, a1, qw[w], kw[w]);
             }
             float part = a0 + a1;
             if constexpr (MULTI) {
@@ -670,8 +702,16 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
                 load_words<NW>(vw, tap_ptr(vb + row[j], col[i]));
             }
             const typename DT<T>::Bcast am = DT<T>::aw_tap(aw, j * SIDE + i);
+            if constexpr (EPW == 1) {
+                // float32: two channels per packed fused multiply-add
 #pragma unroll
-            for (int w = 0; w < NW; ++w) DT<T>::wmul(am, vw[w], &o[w * EPW]);
+                for (int w = 0; w < NW; w += 2)
+                    fma_f32x2(o[w], o[w + 1], __uint_as_float(aw[j * SIDE + i]), __uint_as_float(vw[w]), __uint_as_float(vw[w + 1]));
+                (void)am;
+            } else {
+#pragma unroll
+                for (int w = 0; w < NW; ++w) DT<T>::wmul(am, vw[w], &o[w * EPW]);
+            }
         }
 
     if (valid) {
