@@ -38,6 +38,7 @@ WORKLOADS = {
     "op_384x384_b4_h8x16_r1_f16_smooth": (4, 384, 384, 8, 16, 1, torch.float16, "self", 3.0, 0.0, True),
     "op_384x384_b1_h8x16_r1_f16_flow": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, False),
     "op_384x384_b1_h8x16_r1_f16_smooth": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 3.0, 0.0, False),
+    "op_384x384_b1_h8x16_r1_f16_flow_perhead": (1, 384, 384, 8, 16, 1, torch.float16, "flow", 24.0, 0.1, True),
     "op_96x96_b2_h4x32_r2_f16_self": (2, 96, 96, 4, 32, 2, torch.float16, "self", 3.0, 0.0, True),      # 1/16 stage of MatchStereo-T
     "op_48x48_b2_h4x40_r2_f16_self": (2, 48, 48, 4, 40, 2, torch.float16, "self", 3.0, 0.0, True),      # 1/32 stage
     "op_104x208_b1_h8x16_r1_f32_cross": (1, 104, 208, 8, 16, 1, torch.float32, "cross", 16.0, 0.0, False),
