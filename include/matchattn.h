@@ -121,6 +121,10 @@ MATCHATTN_API int matchattn_fused_forward_ex(const void *max_offset, const void 
  *                    multiplied by it element-wise;
  *   out_row_stride   elements from one query's out to the next (0 = h*hd);
  *   attn_row_stride  elements from one query's attn_out to the next (0 = h*(2r+2)^2).
+ *   kv_item_shift    keys and values of batch item b are read from item (b + kv_item_shift) mod B
+ *                    (0 <= kv_item_shift < B).  The cross branch pairs every view with the other one
+ *                    (models/attention_blocks.py:67-71: tgt = cat((tgt_, ref_))); with B/2 here the caller
+ *                    projects K and V of the un-swapped batch and skips that copy.
  * With out = buf, attn_out = buf + h*hd and both strides = h*hd + h*(2r+2)^2 the kernel writes
  * the concatenated [B, Nq, h*hd + h*(2r+2)^2] tensor the projection consumes.  Direct kernel only.
  */
@@ -130,7 +134,7 @@ MATCHATTN_API int matchattn_fused_forward_glue(const void *max_offset, const voi
                                                int dtype, int attn_type, float scale,
                                                int q_row_begin, int q_row_end,
                                                int clamp_offsets, long long out_row_stride,
-                                               long long attn_row_stride, void *cuda_stream);
+                                               long long attn_row_stride, int kv_item_shift, void *cuda_stream);
 
 /*
  * The operator with every index checked on the device: the debugging aid for hosts that cannot run a

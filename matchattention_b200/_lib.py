@@ -46,7 +46,7 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_fused_backward.argtypes = [_vp] * 10 + [_i] * 9 + [_f, _i, _i, _vp]
     lib.matchattn_fused_forward_glue.restype = _i
     lib.matchattn_fused_forward_glue.argtypes = [_vp] * 7 + [_i] * 9 + [_f, _i, _i, _i, ctypes.c_longlong,
-                                                 ctypes.c_longlong, _vp]
+                                                 ctypes.c_longlong, _i, _vp]
     lib.matchattn_upsample_field.restype = _i
     lib.matchattn_upsample_field.argtypes = [_vp] * 3 + [_i] * 6 + [_vp]
     lib.matchattn_stereo_volume.restype = _i

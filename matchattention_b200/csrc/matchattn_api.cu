@@ -281,6 +281,7 @@ struct Glue {
     int clamp = 0;
     long long out_stride = 0, attn_stride = 0;      // 0 = natural
     unsigned long long *debug = nullptr;            // checked entry point: status words
+    int kv_shift = 0;                               // keys / values of item b come from item (b + kv_shift) mod B
 };
 
 int forward_impl(const void *max_offset, const void *q, const void *k, const void *v, void *out, void *attn_out,
@@ -309,7 +310,7 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     if (out_stride < C || attn_stride < 1LL * h * M || out_stride >= (1LL << 30) || attn_stride >= (1LL << 30))
         return MATCHATTN_ERR_SHAPE;
     const bool has_glue = glue.gate != nullptr || glue.clamp != 0 || out_stride != C || attn_stride != 1LL * h * M ||
-                          glue.debug != nullptr;
+                          glue.debug != nullptr || glue.kv_shift != 0;
     if (has_glue && (strategy == kStrategyBinned || variant == kVariantMma || variant == kVariantMma2)) return MATCHATTN_ERR_VARIANT;
     if (!aligned(glue.gate, esize)) return MATCHATTN_ERR_ALIGN;
     if (!aligned(max_offset, 2 * esize) || !aligned(q, esize) || !aligned(k, esize) || !aligned(v, esize) ||
@@ -360,6 +361,7 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     p.attn_stride = static_cast<int>(attn_stride);
     p.clamp = glue.clamp;
     p.debug = glue.debug;
+    p.kv_shift = glue.kv_shift;
     if (glue.clamp) {
         // the caller's bounds (models/attention_blocks.py:49-52), rounded to the tensor type as there
         const float hx = static_cast<float>(W - 1 - r - 1e-3), hy = static_cast<float>(H - 1 - r - 1e-3);
@@ -480,9 +482,11 @@ int matchattn_fused_forward_glue(const void *max_offset, const void *q, const vo
                                  const void *gate, void *out, void *attn_out, int B, int H, int W, int h, int hd,
                                  int rx, int ry, int dtype, int attn_type, float scale, int q_row_begin,
                                  int q_row_end, int clamp_offsets, long long out_row_stride,
-                                 long long attn_row_stride, void *cuda_stream)
+                                 long long attn_row_stride, int kv_item_shift, void *cuda_stream)
 {
+    if (kv_item_shift < 0 || kv_item_shift >= (B > 0 ? B : 1)) return MATCHATTN_ERR_SHAPE;
     matchattn::Glue glue;
+    glue.kv_shift = kv_item_shift;
     glue.gate = gate;
     glue.clamp = clamp_offsets;
     glue.out_stride = out_row_stride;
@@ -540,7 +544,7 @@ const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int poi
     return text;
 }
 
-int matchattn_version(void) { return 100; }
+int matchattn_version(void) { return 101; }
 
 const char *matchattn_strerror(int status)
 {

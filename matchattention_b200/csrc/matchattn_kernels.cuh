@@ -58,6 +58,7 @@ struct Params {
     float clamp_lo, clamp_hi_x, clamp_hi_y;   // bounds, already rounded to T
     int scale_pow2;          // non-zero: 16-bit type and `scale` is a power of two that the type represents exactly
     unsigned long long *debug;   // when not null (checked entry point): [0] counts out-of-range indices, [1] keeps the first
+    int kv_shift;            // keys / values of batch item b are read from item (b + kv_shift) mod B (0: the same item)
 };
 
 // Records an index that left its array (checked entry point only): a count and the first offender as
@@ -604,7 +605,9 @@ __global__ void __launch_bounds__(kThreads, min_blocks<T, R, CPL>()) fused_forwa
     }
 
     const int lane_off = head * p.hd + sl * SLICE;
-    const int64_t kv_base = static_cast<int64_t>(b) * p.N * p.C + lane_off;
+    // the cross branch reads the other view's keys / values: the caller's batch roll folded into the index
+    const int b_kv = (EXTRAS && p.kv_shift != 0) ? (b + p.kv_shift >= p.B ? b + p.kv_shift - p.B : b + p.kv_shift) : b;
+    const int64_t kv_base = static_cast<int64_t>(b_kv) * p.N * p.C + lane_off;
     const T *kb = static_cast<const T *>(p.k) + kv_base;
     const T *vb = static_cast<const T *>(p.v) + kv_base;
 
@@ -779,7 +782,8 @@ __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params 
     const int x0 = window_origin(xf, r, p.W) - r, y0 = window_origin(yf, r, p.H) - r;
 
     const T *qp = static_cast<const T *>(p.q) + bq * p.C + head * p.hd;
-    const int64_t kv_base = static_cast<int64_t>(b) * p.N * p.C + head * p.hd;
+    const int b_kv = b + p.kv_shift >= p.B ? b + p.kv_shift - p.B : b + p.kv_shift;
+    const int64_t kv_base = static_cast<int64_t>(b_kv) * p.N * p.C + head * p.hd;
     const T *kb = static_cast<const T *>(p.k) + kv_base;
     const T *vb = static_cast<const T *>(p.v) + kv_base;
 

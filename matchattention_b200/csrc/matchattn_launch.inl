@@ -12,7 +12,7 @@ namespace matchattn {
 template <typename T, int R>
 static cudaError_t launch_fast_r(const Params &p, int cpl, bool multi, dim3 grid, int threads, cudaStream_t stream)
 {
-    const bool extras = p.guard != nullptr || p.sorted != nullptr || p.gate != nullptr || p.clamp != 0 || p.debug != nullptr ||
+    const bool extras = p.guard != nullptr || p.sorted != nullptr || p.gate != nullptr || p.clamp != 0 || p.debug != nullptr || p.kv_shift != 0 ||
                         p.out_stride != p.C || p.attn_stride != p.h * (2 * R + 2) * (2 * R + 2);
     // power-of-two scale: a build of the plain kernel that finishes two scores per packed instruction
     constexpr bool kCanPack = sizeof(T) == 2;

@@ -52,10 +52,10 @@ def _make_attention_forward(kn):
         r = self.win_r[0]
         x = x.view(B, N, -1)
         if self.cross:
-            # keys/values of a view come from the other view: project once, swap the batch halves after
-            q, g = self.q(x), self.g(x)
-            k, v = self.k(x).roll(B // 2, 0), self.v(x).roll(B // 2, 0)
-            y = kn.cross(max_offset, q, k, v, g, H, W, r, self.scale, True)
+            # keys/values of a view come from the other view: project the batch as it is, the kernel
+            # reads item (b + B/2) mod B (no copy of K and V)
+            q, g, k, v = self.q(x), self.g(x), self.k(x), self.v(x)
+            y = kn.cross(max_offset, q, k, v, g, H, W, r, self.scale, True, B // 2)
         else:
             if self.noc_embed:
                 x = torch.cat((x, noc_mask.view(B, N, -1)), dim=-1)

@@ -291,7 +291,7 @@ def match_attention_autograd(max_offset, q, k, v, H: int, W: int, r: int, scale:
 # ---- the caller's glue folded into the kernel ------------------------------------------------
 
 def launch_glue(max_offset, q, k, v, gate, out_base, attn_base, H: int, W: int, r: int, scale: float, *,
-                clamp: bool, out_stride: int = 0, attn_stride: int = 0) -> None:
+                clamp: bool, out_stride: int = 0, attn_stride: int = 0, kv_shift: int = 0) -> None:
     """Enqueue the direct kernel with clamp / gate / strided outputs (see matchattn_fused_forward_glue)."""
     B, Nq, C = q.shape
     h = max_offset.size(2)
@@ -309,14 +309,19 @@ def launch_glue(max_offset, q, k, v, gate, out_base, attn_base, H: int, W: int, 
             max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
             gate.data_ptr() if gate is not None else None, out_base, attn_base,
             B, H, W, h, C // h, r, r, _DTYPE_CODE[q.dtype], _lib.L1_NORM, float(scale), 0, H,
-            int(bool(clamp)), int(out_stride), int(attn_stride), torch.cuda.current_stream().cuda_stream)
+            int(bool(clamp)), int(out_stride), int(attn_stride), int(kv_shift),
+            torch.cuda.current_stream().cuda_stream)
     _lib.check(status)
 
 
-def cross_attention_core(max_offset, q, k, v, gate, H: int, W: int, r: int, scale: float, clamp: bool = True):
+def cross_attention_core(max_offset, q, k, v, gate, H: int, W: int, r: int, scale: float, clamp: bool = True,
+                         kv_shift: int = 0):
     """What MatchAttention.forward does between its q/k/v/g projections and its output projection in
     the cross branch (models/attention_blocks.py:79-98), in one kernel: clamp the centres, run the
     operator, multiply by the gate and lay the result out as cat((g * x, attn), -1).
+
+    ``kv_shift`` folds the branch's batch swap in as well: item b attends to the keys / values of item
+    (b + kv_shift) mod B, so with B // 2 the caller passes K and V of the un-swapped batch.
 
     Returns a [B, N, C + h*(2r+2)^2] tensor ready for ``proj``."""
     B, N, C = q.shape
@@ -325,7 +330,7 @@ def cross_attention_core(max_offset, q, k, v, gate, H: int, W: int, r: int, scal
     width = C + h * M
     buf = q.new_empty(B, N, width)
     launch_glue(max_offset, q, k, v, gate, buf.data_ptr(), buf.data_ptr() + C * buf.element_size(), H, W, r, scale,
-                clamp=clamp, out_stride=width, attn_stride=width)
+                clamp=clamp, out_stride=width, attn_stride=width, kv_shift=kv_shift)
     return buf
 
 
@@ -466,13 +471,14 @@ def flow_init(correlation: torch.Tensor, H: int, W: int, return_debug: bool = Fa
 
 @torch.library.custom_op("matchattn_b200::cross_attention_core_op", mutates_args=())
 def cross_attention_core_op(max_offset: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-                            gate: torch.Tensor, H: int, W: int, r: int, scale: float, clamp: bool) -> torch.Tensor:
+                            gate: torch.Tensor, H: int, W: int, r: int, scale: float, clamp: bool,
+                            kv_shift: int) -> torch.Tensor:
     return cross_attention_core(max_offset.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(),
-                                gate.contiguous(), H, W, r, scale, clamp)
+                                gate.contiguous(), H, W, r, scale, clamp, kv_shift)
 
 
 @cross_attention_core_op.register_fake
-def _(max_offset, q, k, v, gate, H, W, r, scale, clamp):
+def _(max_offset, q, k, v, gate, H, W, r, scale, clamp, kv_shift):
     B, N, C = q.shape
     return q.new_empty(B, N, C + max_offset.size(2) * (2 * r + 2) ** 2)
 

@@ -34,6 +34,25 @@ def _worker(rank, world, port, results):
             one_out, one_attn = match_attention(*args, H, W, r, 0.2)
             results.put((bool(torch.equal(out, one_out)), bool(torch.equal(attn, one_attn))))
         dist.barrier()
+        # the resident forms: every rank regenerates the same seeded inputs, keeps its own rows of K / V in
+        # full-size buffers poisoned elsewhere, exchanges all rows (all-gather) or halo rows only
+        from matchattention_b200.band import band_match_attention_resident, band_rows
+        H2 = 64                                                   # divisible by 2 and 4: the in-place all-gather path
+        mo, q, k, v = (t.to(dev) for t in make_inputs(43, B, H2, W, h, hd, r, torch.float16, kind="flow", spread=3.0,
+                                                      border_frac=0.0))
+        one_out, one_attn = match_attention(mo, q, k, v, H2, W, r, 0.2)
+        r0, r1 = band_rows(H2, world, rank)
+        sl = slice(r0 * W, r1 * W)
+        ok = True
+        for max_dy in (None, 4.0):
+            kv = [torch.full_like(k, float("nan")), torch.full_like(v, float("nan"))]
+            kv[0][:, sl], kv[1][:, sl] = k[:, sl], v[:, sl]
+            ob, ab = band_match_attention_resident(mo[:, sl].contiguous(), q[:, sl].contiguous(), kv[0], kv[1], H2, W, r,
+                                                   0.2, max_abs_dy=max_dy)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(ob, one_out[:, sl])) and bool(torch.equal(ab, one_attn[:, sl]))
+        results.put(("resident", rank, ok))
+        dist.barrier()
     finally:
         dist.destroy_process_group()
 
@@ -50,4 +69,7 @@ def test_band_split_over_nccl_equals_single_gpu():
     for p in procs:
         p.join(timeout=300)
         assert p.exitcode == 0
-    assert results.get(timeout=5) == (True, True)
+    got = [results.get(timeout=5) for _ in range(world + 1)]
+    assert (True, True) in got
+    assert sorted(g[1] for g in got if g[0] == "resident") == list(range(world))
+    assert all(g[2] for g in got if g[0] == "resident")

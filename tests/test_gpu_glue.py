@@ -56,3 +56,18 @@ def test_fused_clamp_equals_separate_clamp_bitwise():
     fused = ma.cross_attention_core(raw, q, k, v, None, H, W, r, 0.25)
     assert torch.equal(fused[..., :h * hd], sep_out)
     assert torch.equal(fused[..., h * hd:], sep_attn.view(B, H * W, -1))
+
+
+@pytest.mark.parametrize("case", [(4, 20, 22, 8, 16, 1), (2, 16, 18, 4, 40, 2), (2, 12, 14, 3, 12, 1)])
+def test_batch_swap_folded_into_the_kernel(case):
+    """kv_shift = B/2 reads the other view's keys / values: bit-identical to rolling K and V first."""
+    import matchattention_b200 as ma
+    B, H, W, h, hd, r = case
+    raw, q, k, v = (t.cuda() for t in make_inputs(92, B, H, W, h, hd, r, torch.float16, kind="raw"))
+    gate = torch.rand_like(q)
+    want = ma.cross_attention_core(raw, q, k.roll(B // 2, 0).contiguous(), v.roll(B // 2, 0).contiguous(), gate, H, W,
+                                   r, hd ** -0.5)
+    got = ma.cross_attention_core(raw, q, k, v, gate, H, W, r, hd ** -0.5, kv_shift=B // 2)
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        ma.cross_attention_core(raw, q, k, v, gate, H, W, r, hd ** -0.5, kv_shift=B)
