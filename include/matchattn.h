@@ -193,10 +193,12 @@ MATCHATTN_API int matchattn_fused_backward(const void *max_offset, const void *q
  *                    3 = the sorting passes only, then the direct kernel walking the queries
  *                        in sorted order (the tiles are then shared through L1 instead of
  *                        shared memory; heads may look at different places).
- *                    5 = staged tiles: every block takes a tile of 16 x QH queries, finds the extent of
- *                        their windows and, when it fits the block's shared-memory region, has the tensor
- *                        memory accelerator copy that K region (then the V region) in with one
- *                        cp.async.bulk.tensor each; taps are then read from shared memory.  A tile whose
+ *                    5, 6 = staged tiles: per tile of 16 x QH queries the extent of the windows is found
+ *                        and, when it fits the shared-memory region, the tensor memory accelerator copies
+ *                        that K region and V region in with one cp.async.bulk.tensor each (completion on an
+ *                        mbarrier); taps are then read from shared memory.  5: one persistent block per SM,
+ *                        a producer warp keeps the next regions arriving while 24 consumer warps compute;
+ *                        6: one block per tile.  A tile whose
  *                        windows spread further is served with global loads by the same block, so every
  *                        input is accepted; it pays when neighbouring queries look at neighbouring places
  *                        (self attention, smooth disparity / flow).  16-bit types, r = 1, head width 8 or

@@ -23,7 +23,7 @@ struct Plan {
 
 constexpr int kVariantAuto = 0, kVariantScalar = 1, kVariantMma = 2, kVariantMma2 = 3;   // 3: two items per lane
 constexpr int kStrategyAuto = 0, kStrategyDirect = 1, kStrategyBinned = 2, kStrategySorted = 3, kStrategySortedMma = 4,
-              kStrategyStaged = 5;
+              kStrategyStaged = 5, kStrategyStagedBlocks = 6;
 
 // Geometry of the binned path; valid == false when the arguments are outside what it covers.
 struct BinGeometry {
@@ -103,6 +103,29 @@ StagedGeometry staged_geometry(int h, int hd, int r, int dtype)
     if (g.ipt > kStagedMaxIPT) g.ipt = kStagedMaxIPT;
     g.QH = g.ipt * g.rows_per_it;
     const long long tokens = static_cast<long long>(kStagedRegionBytes) / (2LL * C);
+    int S = -1;
+    while ((kStagedQW + 3 + 2 * (S + 1)) * 1LL * (g.QH + 3 + 2 * (S + 1)) <= tokens && kStagedQW + 3 + 2 * (S + 1) <= 256 &&
+           g.QH + 3 + 2 * (S + 1) <= 256)
+        ++S;
+    if (S < 0) return g;
+    g.RW = kStagedQW + 3 + 2 * S;
+    g.RH = g.QH + 3 + 2 * S;
+    g.valid = true;
+    return g;
+}
+
+// Tile and region of the persistent staged kernel: 768 (query, head) items per tile, 16 queries wide.
+StagedGeometry persist_geometry(int h, int hd, int r, int dtype)
+{
+    StagedGeometry g{};
+    if (dtype == MATCHATTN_F32 || r != 1 || (hd != 8 && hd != 16)) return g;
+    if (h != 1 && h != 2 && h != 4 && h != 8 && h != 16) return g;
+    const int C = h * hd;
+    if (C > 256) return g;
+    g.ipt = 1;
+    g.rows_per_it = (kPersistConsumers / h) / kStagedQW;
+    g.QH = g.rows_per_it;
+    const long long tokens = static_cast<long long>(kPersistRegionBytes) / (2LL * C);
     int S = -1;
     while ((kStagedQW + 3 + 2 * (S + 1)) * 1LL * (g.QH + 3 + 2 * (S + 1)) <= tokens && kStagedQW + 3 + 2 * (S + 1) <= 256 &&
            g.QH + 3 + 2 * (S + 1) <= 256)
@@ -373,8 +396,39 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     }
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
 
-    // staged path: K/V tiles copied to shared memory by the tensor memory accelerator, per tile of queries
+    // staged path, persistent form: one block per SM, a producer warp keeps the K and V regions of the next
+    // tile arriving (cp.async.bulk.tensor on mbarriers) while 24 consumer warps work on the current one
     if (strategy == kStrategyStaged) {
+        const StagedGeometry sg = persist_geometry(h, hd, r, dtype);
+        if (!sg.valid || !pl.fast || pl.lph != 1 || has_glue || !aligned(k, 16) || !aligned(v, 16))
+            return MATCHATTN_ERR_VARIANT;
+        CUtensorMap map_k, map_v;
+        if (!make_kv_map(&map_k, k, dtype, B, H, W, static_cast<int>(C), sg.RW, sg.RH) ||
+            !make_kv_map(&map_v, v, dtype, B, H, W, static_cast<int>(C), sg.RW, sg.RH))
+            return MATCHATTN_ERR_VARIANT;
+        PersistParams sp{};
+        sp.p = p;
+        sp.QH = sg.QH; sp.RW = sg.RW; sp.RH = sg.RH;
+        sp.tiles_x = (W + kStagedQW - 1) / kStagedQW;
+        sp.tiles_y = (p.rows + sg.QH - 1) / sg.QH;
+        sp.total_tiles = 1LL * sp.tiles_x * sp.tiles_y * B;
+        sp.region_bytes = static_cast<uint32_t>(2LL * C * sg.RW * sg.RH);
+        sp.status = nullptr;
+        if (1LL * sp.tiles_x * sp.tiles_y > 2147483647LL) return MATCHATTN_ERR_TOO_LARGE;
+        if (workspace != nullptr && workspace_bytes >= 8 && aligned(workspace, 8)) {
+            sp.status = static_cast<unsigned long long *>(workspace);
+            cudaError_t e = cudaMemsetAsync(workspace, 0, 8, stream);
+            if (e != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(e);
+        }
+        const long long sms = sm_count();
+        const int grid_blocks = static_cast<int>(sp.total_tiles < sms ? sp.total_tiles : sms);
+        cudaError_t err = dtype == MATCHATTN_F16 ? launch_staged_persistent<__half>(sp, pl.cpl, map_k, map_v, grid_blocks, stream)
+                                                 : launch_staged_persistent<__nv_bfloat16>(sp, pl.cpl, map_k, map_v, grid_blocks, stream);
+        return err == cudaSuccess ? MATCHATTN_OK : MATCHATTN_ERR_CUDA + static_cast<int>(err);
+    }
+
+    // staged path, one block per tile (two blocks per SM; kept for comparison, strategy 6)
+    if (strategy == kStrategyStagedBlocks) {
         const StagedGeometry sg = staged_geometry(h, hd, r, dtype);
         if (!sg.valid || !pl.fast || pl.lph != 1 || has_glue || !aligned(k, 16) || !aligned(v, 16) || H > 65535 * 8)
             return MATCHATTN_ERR_VARIANT;

@@ -123,6 +123,30 @@ static cudaError_t launch_staged_one(const StagedParams &sp, const CUtensorMap &
     return cudaGetLastError();
 }
 
+template <typename T, int CPL, bool POW2>
+static cudaError_t launch_persist_one(const PersistParams &sp, const CUtensorMap &map_k, const CUtensorMap &map_v,
+                                      int grid_blocks, cudaStream_t stream)
+{
+    const size_t smem_bytes = 2 * kPersistRegionBytes + 128;
+    cudaError_t e = cudaFuncSetAttribute(staged_persistent_kernel<T, CPL, POW2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem_bytes));
+    if (e != cudaSuccess) return e;
+    staged_persistent_kernel<T, CPL, POW2><<<grid_blocks, kPersistThreads, smem_bytes, stream>>>(sp, map_k, map_v);
+    return cudaGetLastError();
+}
+
+template <>
+cudaError_t launch_staged_persistent<MATCHATTN_T>(const PersistParams &sp, int cpl, const CUtensorMap &map_k,
+                                                  const CUtensorMap &map_v, int grid_blocks, cudaStream_t stream)
+{
+    const bool pow2 = sp.p.scale_pow2 != 0;
+    if (cpl == 1) return pow2 ? launch_persist_one<MATCHATTN_T, 1, true>(sp, map_k, map_v, grid_blocks, stream)
+                              : launch_persist_one<MATCHATTN_T, 1, false>(sp, map_k, map_v, grid_blocks, stream);
+    if (cpl == 2) return pow2 ? launch_persist_one<MATCHATTN_T, 2, true>(sp, map_k, map_v, grid_blocks, stream)
+                              : launch_persist_one<MATCHATTN_T, 2, false>(sp, map_k, map_v, grid_blocks, stream);
+    return cudaErrorInvalidValue;
+}
+
 template <>
 cudaError_t launch_staged<MATCHATTN_T>(const StagedParams &sp, int cpl, const CUtensorMap &map_k, const CUtensorMap &map_v,
                                        dim3 grid, size_t smem_bytes, cudaStream_t stream)

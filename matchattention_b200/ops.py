@@ -74,6 +74,7 @@ def _check_tensors(max_offset, q, k, v, output, attn_out, H, W, rows, attn_num):
 
 STRATEGY_AUTO, STRATEGY_DIRECT, STRATEGY_BINNED = 0, 1, 2
 STRATEGY_STAGED = 5
+STRATEGY_STAGED_BLOCKS = 6
 
 # scratch for the binned path, one buffer per (device, stream): calls on one stream are ordered, so
 # they can share it; calls on different streams may overlap on the device and must not
@@ -139,7 +140,7 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
         elif strategy == STRATEGY_AUTO and workspace is None:
             # the library's own choice needs no scratch: nothing is looked up or allocated here
             status = _lib.lib.matchattn_fused_forward(*args)
-        elif strategy == STRATEGY_STAGED:
+        elif strategy in (STRATEGY_STAGED, STRATEGY_STAGED_BLOCKS):
             # needs no scratch; an 8-byte workspace, if given, receives the number of tiles that were
             # served by global loads because their windows did not fit the staged region
             ws_ptr, ws_len = (workspace.data_ptr(), workspace.numel()) if workspace is not None else (None, 0)
