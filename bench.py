@@ -1020,6 +1020,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": ncu_traffic_per_launch(args.workload), "peak_kind": peak_kind,
                          "algorithmic_bytes_per_query": bpq, "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "frac_first_k_steps": bpq * B * H * W / (once_ms / args.steps * 1e-3) / 1e9 / peak,
                          "kernel": ma.describe_dispatch(h, hd, r, dtype)},
             "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
             "timed_region": {"k_step_repeats": reps, "seconds": ms_total * 1e-3,
