@@ -8,10 +8,18 @@ token map (a 1536x1536 pair at 1/4 resolution), C=128 as 8 heads x 16, 3x3
 sub-windows (r=1), float16, flow-like offsets uniform in +-24 tokens shared by
 the heads, 10 % of the queries left unclamped next to a border.  With N GPUs
 every rank processes its own batch (independent pairs, no collective): weak
-scaling.  Rank 0 prints ONE JSON line.
+scaling.  Rank 0 prints ONE JSON line: the device-resident throughput (`value`,
+sustained over at least 0.3 s) with its roofline, the other configuration shapes
+(`shapes`), the end-to-end throughput from pinned host buffers (`e2e`, with a
+copy-only leg), the reference's own PyTorch path timed on the host cores
+(`cpu_baseline`), at one GPU the reference's MatchStereo-T forward with this
+library's kernels (`model`, ms per pair), and with several GPUs the row-band
+split of one very large pair (`band`).
 
-`--impl reference` times the CPU restatement of the reference's algorithm
-(oracle/) on the host cores instead, on a bounded sample of the same workload.
+`--impl reference` times the reference's own CPU implementation of the path (the
+unmodified copy under oracle/_ref/, else the C restatement) on the host cores,
+on a bounded sample of the same workload.  `--mode` selects the other
+measurements (model, model_ops, band, upsample, volume).
 """
 from __future__ import annotations
 
