@@ -111,66 +111,94 @@ __global__ void __launch_bounds__(kFlowThreads) flow_transposed_softmax_kernel(c
     }
 }
 
-// per (b2, i): maximum over j of the 5 x 5 box average of prob[b2] around (i, j), and its first arg max
+// per (b2, i): maximum over j of the 5 x 5 box average of prob[b2] around (i, j), and its first arg max.
+// A block takes kPoolRows consecutive rows i: the kPoolRows + 4 rows of probabilities they need are staged
+// once per column chunk in shared memory (1.5 reads per element instead of 5), every thread keeps the
+// 12 x 5 neighbourhood of its column in registers and forms the 25-term sums of its eight outputs from
+// them, in the reference's order (row-major over the window, out-of-range taps skipped).
+constexpr int kPoolRows = 8;
+
 template <typename T>
 __global__ void __launch_bounds__(kFlowThreads) flow_pool_argmax_kernel(const T *__restrict__ prob, T *__restrict__ blur_max,
                                                                          int *__restrict__ arg_out, int64_t N)
 {
-    __shared__ float rows[5][kFlowThreads + 4];
-    __shared__ float best_v[kFlowThreads / 32];
-    __shared__ int best_j[kFlowThreads / 32];
-    const int64_t i = blockIdx.x;
+    __shared__ float rows[kPoolRows + 4][kFlowThreads + 4];
+    __shared__ float best_v[kPoolRows][kFlowThreads / 32];
+    __shared__ int best_j[kPoolRows][kFlowThreads / 32];
+    const int64_t i0 = static_cast<int64_t>(blockIdx.x) * kPoolRows;
     const T *base = prob + static_cast<int64_t>(blockIdx.y) * N * N;
-    float best = -INFINITY;
-    int arg = 0x7fffffff;
+    float best[kPoolRows];
+    int arg[kPoolRows];
+#pragma unroll
+    for (int r = 0; r < kPoolRows; ++r) {
+        best[r] = -INFINITY;
+        arg[r] = 0x7fffffff;
+    }
     for (int64_t c0 = 0; c0 < N; c0 += kFlowThreads) {
-        for (int e = threadIdx.x; e < 5 * (kFlowThreads + 4); e += kFlowThreads) {
+        for (int e = threadIdx.x; e < (kPoolRows + 4) * (kFlowThreads + 4); e += kFlowThreads) {
             const int di = e / (kFlowThreads + 4), cc = e - di * (kFlowThreads + 4);
-            const int64_t ii = i + di - 2, jj = c0 + cc - 2;
+            const int64_t ii = i0 + di - 2, jj = c0 + cc - 2;
             rows[di][cc] = (ii >= 0 && ii < N && jj >= 0 && jj < N) ? load_one<T>(base + ii * N + jj) : 0.f;
         }
         __syncthreads();
         const int64_t j = c0 + threadIdx.x;
         if (j < N) {
-            // the sum runs over the window in row-major order, out-of-range taps skipped, as the pooling kernel adds
-            float acc = 0.f;
+            float w[kPoolRows + 4][5];
 #pragma unroll
-            for (int di = 0; di < 5; ++di)
+            for (int di = 0; di < kPoolRows + 4; ++di)
 #pragma unroll
-                for (int dj = 0; dj < 5; ++dj) {
-                    const int64_t ii = i + di - 2, jj = j + dj - 2;
-                    if (ii >= 0 && ii < N && jj >= 0 && jj < N) acc += rows[di][threadIdx.x + dj];
+                for (int dj = 0; dj < 5; ++dj) w[di][dj] = rows[di][threadIdx.x + dj];
+#pragma unroll
+            for (int r = 0; r < kPoolRows; ++r) {
+                const int64_t i = i0 + r;
+                if (i >= N) break;
+                float acc = 0.f;
+#pragma unroll
+                for (int di = 0; di < 5; ++di)
+#pragma unroll
+                    for (int dj = 0; dj < 5; ++dj) {
+                        const int64_t ii = i + di - 2, jj = j + dj - 2;
+                        if (ii >= 0 && ii < N && jj >= 0 && jj < N) acc += w[r + di][dj];
+                    }
+                const float bl = DT<T>::rnd(__fdiv_rn(acc, 25.f));
+                if (bl > best[r]) {
+                    best[r] = bl;
+                    arg[r] = static_cast<int>(j);
                 }
-            const float bl = DT<T>::rnd(__fdiv_rn(acc, 25.f));
-            if (bl > best) {
-                best = bl;
-                arg = static_cast<int>(j);
             }
         }
         __syncthreads();
     }
-    // block arg max: larger value wins, equal values keep the smaller index
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oj = __shfl_xor_sync(0xffffffffu, arg, o);
-        if (ov > best || (ov == best && oj < arg)) {
-            best = ov;
-            arg = oj;
+    // block arg max per row: larger value wins, equal values keep the smaller index
+#pragma unroll
+    for (int r = 0; r < kPoolRows; ++r) {
+        float bv = best[r];
+        int bj = arg[r];
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
+            if (ov > bv || (ov == bv && oj < bj)) {
+                bv = ov;
+                bj = oj;
+            }
+        }
+        if ((threadIdx.x & 31) == 0) {
+            best_v[r][threadIdx.x >> 5] = bv;
+            best_j[r][threadIdx.x >> 5] = bj;
         }
     }
-    if ((threadIdx.x & 31) == 0) {
-        best_v[threadIdx.x >> 5] = best;
-        best_j[threadIdx.x >> 5] = arg;
-    }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < kPoolRows && i0 + threadIdx.x < N) {
+        const int r = threadIdx.x;
+        float bv = best_v[r][0];
+        int bj = best_j[r][0];
         for (int w = 1; w < kFlowThreads / 32; ++w)
-            if (best_v[w] > best || (best_v[w] == best && best_j[w] < arg)) {
-                best = best_v[w];
-                arg = best_j[w];
+            if (best_v[r][w] > bv || (best_v[r][w] == bv && best_j[r][w] < bj)) {
+                bv = best_v[r][w];
+                bj = best_j[r][w];
             }
-        arg_out[blockIdx.y * N + i] = arg;
-        if (blur_max != nullptr) store_one<T>(blur_max + blockIdx.y * N + i, best);
+        arg_out[blockIdx.y * N + i0 + r] = bj;
+        if (blur_max != nullptr) store_one<T>(blur_max + blockIdx.y * N + i0 + r, bv);
     }
 }
 
@@ -222,7 +250,8 @@ cudaError_t run_flow_init(const void *corr_, void *prob_, void *flow_, void *blu
     flow_col_stats_kernel<T><<<dim3(static_cast<unsigned>((N + 63) / 64), B), kFlowThreads, 0, stream>>>(corr, cmax, csum, N);
     const unsigned tiles = static_cast<unsigned>((N + 31) / 32);
     flow_transposed_softmax_kernel<T><<<dim3(tiles, tiles, B), kFlowThreads, 0, stream>>>(corr, cmax, csum, prob + B * N * N, N);
-    flow_pool_argmax_kernel<T><<<dim3(static_cast<unsigned>(N), 2 * B), kFlowThreads, 0, stream>>>(prob, static_cast<T *>(blur_), arg, N);
+    flow_pool_argmax_kernel<T><<<dim3(static_cast<unsigned>((N + kPoolRows - 1) / kPoolRows), 2 * B), kFlowThreads, 0, stream>>>(
+        prob, static_cast<T *>(blur_), arg, N);
     const int64_t total = 2 * B * N;
     flow_window_kernel<T><<<static_cast<unsigned>((total + kFlowThreads - 1) / kFlowThreads), kFlowThreads, 0, stream>>>(
         prob, arg, static_cast<T *>(flow_), centre, H, W, total, tiny);
