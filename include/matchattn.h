@@ -38,10 +38,15 @@ extern "C" {
 #define MATCHATTN_F16  1
 #define MATCHATTN_BF16 2
 
-/* scoring functions (argument `attn_type`).  Only the negative L1 distance is
- * implemented; it is the only one the reference models select
- * (models/attention_blocks.py:93). */
-#define MATCHATTN_L1_NORM 0
+/* scoring functions (argument `attn_type`).  The negative L1 distance is the
+ * only one the reference models select (models/attention_blocks.py:93) and the
+ * one the tuned kernels compute.  The dot product exists in the reference only
+ * as an unused native kernel (models/src/match_former_fused_forward.cu:222-251)
+ * with no PyTorch form to compare with; here it runs on the general kernel
+ * (any head width, one thread per query and head; no tuned variant, no
+ * strategy other than 0 or 1), checked against a restatement of that kernel. */
+#define MATCHATTN_L1_NORM     0
+#define MATCHATTN_DOT_PRODUCT 1
 
 /* status codes */
 #define MATCHATTN_OK                 0
@@ -49,7 +54,7 @@ extern "C" {
 #define MATCHATTN_ERR_SHAPE          2  /* a size is <= 0, or the row band is empty / outside */
 #define MATCHATTN_ERR_WINDOW_FIT     3  /* 2r+2 exceeds H or W (models/attention_blocks.py:64) */
 #define MATCHATTN_ERR_DTYPE          4  /* unknown element type                               */
-#define MATCHATTN_ERR_ATTN_TYPE      5  /* scoring function not implemented                   */
+#define MATCHATTN_ERR_ATTN_TYPE      5  /* unknown scoring function                            */
 #define MATCHATTN_ERR_WINDOW         6  /* rx != ry, r < 0 or r above the supported maximum    */
 #define MATCHATTN_ERR_ALIGN          7  /* a pointer is not aligned to its element size       */
 #define MATCHATTN_ERR_TOO_LARGE      8  /* sizes overflow the 32-bit index ranges in use      */

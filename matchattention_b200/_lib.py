@@ -21,6 +21,8 @@ EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_f
 
 F32, F16, BF16 = 0, 1, 2
 L1_NORM = 0
+DOT_PRODUCT = 1
+ATTN_TYPE_CODE = {"l1_norm": L1_NORM, "dot_product": DOT_PRODUCT}
 
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 

@@ -315,7 +315,12 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
 {
     if (!max_offset || !q || !k || !v || !out) return MATCHATTN_ERR_NULL;
     if (dtype != MATCHATTN_F32 && dtype != MATCHATTN_F16 && dtype != MATCHATTN_BF16) return MATCHATTN_ERR_DTYPE;
-    if (attn_type != MATCHATTN_L1_NORM) return MATCHATTN_ERR_ATTN_TYPE;
+    if (attn_type != MATCHATTN_L1_NORM && attn_type != MATCHATTN_DOT_PRODUCT) return MATCHATTN_ERR_ATTN_TYPE;
+    if (attn_type == MATCHATTN_DOT_PRODUCT) {
+        // the dot product runs on the general kernel only
+        if ((strategy != kStrategyAuto && strategy != kStrategyDirect) || variant != 0) return MATCHATTN_ERR_VARIANT;
+        force_generic = 1;
+    }
     if (B <= 0 || H <= 0 || W <= 0 || h <= 0 || hd <= 0) return MATCHATTN_ERR_SHAPE;
     if (q_row_begin < 0 || q_row_end > H || q_row_begin >= q_row_end) return MATCHATTN_ERR_SHAPE;
     if (rx != ry || rx < 0 || rx > MATCHATTN_MAX_R) return MATCHATTN_ERR_WINDOW;
@@ -385,6 +390,7 @@ int forward_impl(const void *max_offset, const void *q, const void *k, const voi
     p.clamp = glue.clamp;
     p.debug = glue.debug;
     p.kv_shift = glue.kv_shift;
+    p.dot = attn_type == MATCHATTN_DOT_PRODUCT;
     if (glue.clamp) {
         // the caller's bounds (models/attention_blocks.py:49-52), rounded to the tensor type as there
         const float hx = static_cast<float>(W - 1 - r - 1e-3), hy = static_cast<float>(H - 1 - r - 1e-3);
@@ -608,7 +614,7 @@ const char *matchattn_strerror(int status)
     case MATCHATTN_ERR_SHAPE: return "bad shape: a size is not positive or the query row band is empty or outside the map";
     case MATCHATTN_ERR_WINDOW_FIT: return "the (2r+2) window does not fit the token map";
     case MATCHATTN_ERR_DTYPE: return "unsupported element type";
-    case MATCHATTN_ERR_ATTN_TYPE: return "unsupported attn_type: only l1_norm is implemented";
+    case MATCHATTN_ERR_ATTN_TYPE: return "attn_type: unknown, or not covered by this entry point (forward: l1_norm 0, dot_product 1; backward: l1_norm)";
     case MATCHATTN_ERR_WINDOW: return "unsupported window: rx must equal ry and 0 <= r <= 4";
     case MATCHATTN_ERR_ALIGN: return "a pointer is not aligned to its element size";
     case MATCHATTN_ERR_TOO_LARGE: return "sizes exceed the supported index range";

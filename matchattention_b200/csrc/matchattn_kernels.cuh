@@ -59,6 +59,7 @@ struct Params {
     int scale_pow2;          // non-zero: 16-bit type and `scale` is a power of two that the type represents exactly
     unsigned long long *debug;   // when not null (checked entry point): [0] counts out-of-range indices, [1] keeps the first
     int kv_shift;            // keys / values of batch item b are read from item (b + kv_shift) mod B (0: the same item)
+    int dot;                 // non-zero: scores are sum(q*k) instead of -sum|q-k| (general kernel only)
 };
 
 // Records an index that left its array (checked entry point only): a count and the first offender as
@@ -795,7 +796,11 @@ __global__ void __launch_bounds__(kThreads) generic_forward_kernel(const Params 
             if (p.debug != nullptr && (ty < 0 || ty >= p.H || tx < 0 || tx >= p.W)) debug_record(p.debug, 1u);
             const T *kp = kb + static_cast<int64_t>(ty * p.W + tx) * p.C;
             float acc = 0.f;
-            for (int c = 0; c < p.hd; ++c) acc += fabsf(DT<T>::rnd(load_one<T>(qp + c) - load_one<T>(kp + c)));
+            if (p.dot) {     // products rounded to T, summed in float32; finish_score negates its argument
+                for (int c = 0; c < p.hd; ++c) acc -= DT<T>::rnd(__fmul_rn(load_one<T>(qp + c), load_one<T>(kp + c)));
+            } else {
+                for (int c = 0; c < p.hd; ++c) acc += fabsf(DT<T>::rnd(load_one<T>(qp + c) - load_one<T>(kp + c)));
+            }
             s[j * side + i] = finish_score<T>(acc, p.scale);
             a[j * side + i] = 0.f;
         }

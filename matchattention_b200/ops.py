@@ -119,8 +119,8 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
     rx, ry = _window_radius(win_r)
     if q_row_end is None:
         q_row_end = H
-    if attn_type != "l1_norm":
-        raise NotImplementedError(f"attn_type {attn_type!r}: only 'l1_norm' is implemented")
+    if attn_type not in _lib.ATTN_TYPE_CODE:
+        raise NotImplementedError(f"attn_type {attn_type!r}: 'l1_norm' and 'dot_product' exist")
     attn_num = (2 * rx + 2) * (2 * ry + 2)
     B, h, hd = _check_tensors(max_offset, q, k, v, output, attn_out, H, W, q_row_end - q_row_begin, attn_num)
     knobs = tile_w or force_generic or chunks_per_lane or variant
@@ -132,7 +132,7 @@ def launch(max_offset, q, k, v, output, attn_out, H: int, W: int, win_r, attn_ty
         stream = torch.cuda.current_stream().cuda_stream
         args = (max_offset.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
                 attn_out.data_ptr() if attn_out is not None else None,
-                B, H, W, h, hd, rx, ry, _DTYPE_CODE[q.dtype], _lib.L1_NORM, float(scale),
+                B, H, W, h, hd, rx, ry, _DTYPE_CODE[q.dtype], _lib.ATTN_TYPE_CODE[attn_type], float(scale),
                 q_row_begin, q_row_end, stream)
         if knobs or strategy == STRATEGY_DIRECT:
             status = _lib.lib.matchattn_fused_forward_ex(*args, int(tile_w), int(bool(force_generic)),
@@ -227,7 +227,8 @@ class MF_FusedForwardOps(nn.Module):
 
 
 def match_attention(max_offset, q, k, v, H: int, W: int, r: int, scale: float, *, need_attn: bool = True,
-                    q_row_begin: int = 0, q_row_end: Optional[int] = None, out=None, attn_out=None, **knobs):
+                    q_row_begin: int = 0, q_row_end: Optional[int] = None, out=None, attn_out=None,
+                    attn_type: str = "l1_norm", **knobs):
     """Functional form: allocates (or reuses) the outputs and returns (out, attn or None)."""
     B, Nq, _ = q.shape
     h = max_offset.size(2)
@@ -235,7 +236,7 @@ def match_attention(max_offset, q, k, v, H: int, W: int, r: int, scale: float, *
         out = torch.empty_like(q)
     if need_attn and attn_out is None:
         attn_out = q.new_empty([B, Nq, h, (2 * r + 2) ** 2])
-    launch(max_offset, q, k, v, out, attn_out if need_attn else None, H, W, (r, r), "l1_norm", scale,
+    launch(max_offset, q, k, v, out, attn_out if need_attn else None, H, W, (r, r), attn_type, scale,
            q_row_begin, q_row_end, **knobs)
     return out, (attn_out if need_attn else None)
 

@@ -156,7 +156,7 @@ static inline int clampi(int a, int lo, int hi) { return a < lo ? lo : (a > hi ?
 static inline __attribute__((always_inline)) void
 one_query_head(const void *mo, const void *q, const void *k, const void *v, void *out, void *attn_out,
                int64_t bq /* b*Nq + nq */, int64_t kbase /* b*H*W */, int head,
-               int H, int W, int h, int hd, int r, float scale, const int dt)
+               int H, int W, int h, int hd, int r, float scale, const int dt, const int dot)
 {
     const int side = 2 * r + 2, sub = 2 * r + 1, M = side * side;
     const int C = h * hd;
@@ -179,15 +179,24 @@ one_query_head(const void *mo, const void *q, const void *k, const void *v, void
         }
     }
 
-    /* models/mat_pytorch_impl.py:74 then models/attention_blocks.py:86 */
+    /* models/mat_pytorch_impl.py:74 then models/attention_blocks.py:86.  dot != 0: the dot-product
+     * scoring of models/src/match_former_fused_forward.cu:222-251, which has no PyTorch counterpart in the
+     * reference (PARITY UNPINNED for it): line 74 restated as (q.unsqueeze(3) * k_sampled).sum(-1), each
+     * product rounded to the tensor type, the sum accumulated in float32. */
     float score[MA_MAX_TAPS];
     const int64_t qoff = bq * C + (int64_t)head * hd;
     for (int m = 0; m < M; ++m) {
         const int64_t koff = tap_tok[m] * C + (int64_t)head * hd;
         float acc = 0.0f;
-        for (int c = 0; c < hd; ++c)
-            acc += fabsf(RND(load_elem(q, qoff + c, dt) - load_elem(k, koff + c, dt)));
-        score[m] = RND(RND(-RND(acc)) * scale);
+        if (dot) {
+            for (int c = 0; c < hd; ++c)     /* built with -ffp-contract=off: product and sum stay separate */
+                acc += RND(load_elem(q, qoff + c, dt) * load_elem(k, koff + c, dt));
+            score[m] = RND(RND(acc) * scale);
+        } else {
+            for (int c = 0; c < hd; ++c)
+                acc += fabsf(RND(load_elem(q, qoff + c, dt) - load_elem(k, koff + c, dt)));
+            score[m] = RND(RND(-RND(acc)) * scale);
+        }
     }
 
     /* models/mat_pytorch_impl.py:148-165: sub-window t is shifted by
@@ -238,6 +247,7 @@ const char *matchattn_oracle_strerror(int code)
     case 3: return "window does not fit the token map";
     case 4: return "unsupported dtype";
     case 5: return "window radius too large for the oracle";
+    case 6: return "unknown scoring function";
     default: return "unknown";
     }
 }
@@ -247,7 +257,7 @@ typedef struct {
     const void *mo, *q, *k, *v;
     void *out, *attn_out;
     int64_t first, last, Nq, N;
-    int H, W, h, hd, r, dtype;
+    int H, W, h, hd, r, dtype, dot;
     float scale;
 } ma_job;
 
@@ -260,15 +270,15 @@ static void *run_job(void *arg)
             switch (jb->dtype) {
             case MA_F32:
                 one_query_head(jb->mo, jb->q, jb->k, jb->v, jb->out, jb->attn_out, bq, kbase, head,
-                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_F32);
+                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_F32, jb->dot);
                 break;
             case MA_F16:
                 one_query_head(jb->mo, jb->q, jb->k, jb->v, jb->out, jb->attn_out, bq, kbase, head,
-                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_F16);
+                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_F16, jb->dot);
                 break;
             default:
                 one_query_head(jb->mo, jb->q, jb->k, jb->v, jb->out, jb->attn_out, bq, kbase, head,
-                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_BF16);
+                               jb->H, jb->W, jb->h, jb->hd, jb->r, jb->scale, MA_BF16, jb->dot);
                 break;
             }
         }
@@ -282,13 +292,15 @@ int matchattn_oracle_max_threads(void)
     return n > 0 ? (int)n : 1;
 }
 
-/* Returns 0 on success.  nthreads <= 0 means "all online cores". */
-int matchattn_oracle_forward(const void *max_offset, const void *q, const void *k, const void *v,
-                             void *out, void *attn_out,
-                             int B, int H, int W, int h, int hd, int r, int dtype, float scale,
-                             int q_row_begin, int q_row_end, int nthreads)
+/* Returns 0 on success.  nthreads <= 0 means "all online cores".  attn_type: 0 = negative L1 distance
+ * (the reference's models), 1 = dot product (restated, see one_query_head). */
+int matchattn_oracle_forward_scored(const void *max_offset, const void *q, const void *k, const void *v,
+                                    void *out, void *attn_out,
+                                    int B, int H, int W, int h, int hd, int r, int dtype, int attn_type, float scale,
+                                    int q_row_begin, int q_row_end, int nthreads)
 {
     if (!max_offset || !q || !k || !v || !out) return 1;
+    if (attn_type != 0 && attn_type != 1) return 6;
     if (B <= 0 || H <= 0 || W <= 0 || h <= 0 || hd <= 0 || r < 0) return 2;
     if (q_row_begin < 0 || q_row_end > H || q_row_begin >= q_row_end) return 2;
     if (2 * r + 2 > H || 2 * r + 2 > W) return 3; /* models/attention_blocks.py:64 */
@@ -311,6 +323,7 @@ int matchattn_oracle_forward(const void *max_offset, const void *q, const void *
         jb->last = total * (t + 1) / nthreads;
         jb->Nq = Nq; jb->N = (int64_t)H * W;
         jb->H = H; jb->W = W; jb->h = h; jb->hd = hd; jb->r = r; jb->dtype = dtype; jb->scale = scale;
+        jb->dot = attn_type;
     }
     int started = 0;
     for (int t = 1; t < nthreads; ++t) {
@@ -322,6 +335,15 @@ int matchattn_oracle_forward(const void *max_offset, const void *q, const void *
     for (int t = started + 1; t < nthreads; ++t) run_job(&jobs[t]);
     for (int t = 1; t <= started; ++t) pthread_join(tids[t], NULL);
     return 0;
+}
+
+int matchattn_oracle_forward(const void *max_offset, const void *q, const void *k, const void *v,
+                             void *out, void *attn_out,
+                             int B, int H, int W, int h, int hd, int r, int dtype, float scale,
+                             int q_row_begin, int q_row_end, int nthreads)
+{
+    return matchattn_oracle_forward_scored(max_offset, q, k, v, out, attn_out, B, H, W, h, hd, r, dtype, 0, scale,
+                                           q_row_begin, q_row_end, nthreads);
 }
 
 /*

@@ -31,7 +31,7 @@ def golden_names(pattern="*"):
     """Golden files of the operator (the upsample_* files belong to load_golden_upsample)."""
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, pattern + ".npz")))
     return [n for n in names if not n.startswith(("upsample_", "volume_", "sampled_", "consistency_", "disparity_",
-                                                  "flowinit_", "backward_"))]
+                                                  "flowinit_", "backward_", "dot_"))]
 
 
 def load_golden_arrays(name):

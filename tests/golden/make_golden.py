@@ -336,6 +336,37 @@ def backward_cases(impl):
         print(f"{name}_f32: {os.path.getsize(path) / 1024:.0f} KiB")
 
 
+def dot_product_cases(impl):
+    """Dot-product scoring.  The reference has it only in its native kernel
+    (models/src/match_former_fused_forward.cu:222-251), with no PyTorch counterpart, so PARITY IS UNPINNED
+    for this scoring: the vectors come from the reference's own functions with the one scoring line
+    (models/mat_pytorch_impl.py:74) swapped for the product form, on the keys gathered with the indices the
+    reference's compute_match_attention returns."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    from _cases import make_inputs
+    for name, seed, B, H, W, h, hd, r, kind in (("dot_r1", 111, 2, 9, 11, 4, 16, 1, "flow"),
+                                                ("dot_r2", 112, 1, 8, 9, 2, 24, 2, "raw")):
+        for dtype in (torch.float32, torch.float16, torch.bfloat16):
+            mo, q, k, v = make_inputs(seed, B, H, W, h, hd, r, dtype, kind=kind, spread=3.0, border_frac=0.2,
+                                      per_head=True)
+            # unit-scale scores, so that the 16-bit softmax is not saturated
+            q, k = (q * 0.5).to(dtype), (k * 0.5).to(dtype)
+            scale = hd ** -0.5
+            N, M = H * W, (2 * r + 2) ** 2
+            qh, kh, vh = (t.view(B, N, h, hd) for t in (q, k, v))
+            m_id = torch.floor(mo).to(torch.int32)
+            wgt = impl.compute_bilinear_weights(mo)
+            _, idx = impl.compute_match_attention(qh, kh, m_id, [r, r], H, W)
+            k_sampled = torch.gather(kh.unsqueeze(3).expand(-1, -1, -1, M, -1), dim=1, index=idx)
+            score = (qh.unsqueeze(3) * k_sampled).sum(dim=-1)
+            attn = impl.compute_bilinear_softmax(score * scale, wgt, [r, r])
+            out = impl.attention_aggregate(vh, attn, idx, [r, r])
+            tag = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[dtype]
+            save_case(f"{name}_{tag}", dtype, H, W, h, r, scale, mo, q, k, v, out, attn,
+                      f"seed {seed}, kind {kind}; dot-product scoring restated (parity unpinned), the rest is the "
+                      "reference's mat_pytorch_impl on CPU")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("MATCHATTN_REF"), required="MATCHATTN_REF" not in os.environ,
@@ -344,9 +375,13 @@ def main():
     ap.add_argument("--only-upsample", action="store_true", help="regenerate only the upsample_field vectors")
     ap.add_argument("--only-new", action="store_true", help="only the wide-head and sampled full-size operator vectors")
     ap.add_argument("--only-field-ops", action="store_true", help="only the consistency-mask and disparity vectors")
+    ap.add_argument("--only-dot", action="store_true", help="only the dot-product scoring vectors")
     a = ap.parse_args()
     impl, blocks = import_reference(a.ref)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if a.only_dot:
+        dot_product_cases(impl)
+        return
     if a.only_field_ops:
         field_op_cases(a.ref, blocks)
         flow_init_cases(a.ref)
@@ -367,6 +402,7 @@ def main():
     field_op_cases(a.ref, blocks)
     flow_init_cases(a.ref)
     backward_cases(impl)
+    dot_product_cases(impl)
 
 
 if __name__ == "__main__":

@@ -44,7 +44,7 @@ def test_arguments_are_rejected_on_the_host():
     assert call(B=0) == 2 and call(r0=5, r1=5) == 2 and call(r1=9) == 2
     assert call(H=3, r1=3) == 3
     assert call(dtype=7) == 4
-    assert call(attn_type=1) == 5
+    assert call(attn_type=2) == 5
     assert call(rx=1, ry=2) == 6 and call(rx=5, ry=5, H=32, W=32, r1=32) == 6
     assert call(q=ctypes.c_void_p(4097)) == 7
     assert call(B=70000) == 8

@@ -78,3 +78,25 @@ def test_inference_path_is_untouched_by_autograd_support():
     with torch.no_grad():
         out, attn = ma.MF_FusedForwardOps()(mo, q.requires_grad_(True), k, v, 12, 13, [1, 1], 16, scale=0.25)
     assert not out.requires_grad and out.grad_fn is None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("h,hd,r", [(3, 12, 1), (2, 8, 3), (2, 24, 2), (8, 16, 1)],
+                         ids=["scalar-hd12", "scalar-r3", "vector-hd24-r2", "vector-hd16-r1"])
+def test_backward_kernels_match_the_restatement(h, hd, r):
+    """Both CUDA kernels (one element at a time for any head width and radius; eight channels at a time
+    for head widths that are multiples of 8 and r <= 2) against the float64 plain-loop restatement."""
+    import matchattention_b200 as ma
+    from oracle import matchattn_backward
+    B, H, W = 1, 9, 10
+    mo, q, k, v = make_inputs(57, B, H, W, h, hd, r, torch.float32, kind="flow", spread=3.0, border_frac=0.2,
+                              per_head=True)
+    gen = torch.Generator().manual_seed(58)
+    g_out = torch.randn(q.shape, generator=gen)
+    g_attn = torch.randn(B, H * W, h, (2 * r + 2) ** 2, generator=gen)
+    want = matchattn_backward.backward(mo, q, k, v, g_out, g_attn, H, W, r, hd ** -0.5)
+    leaves = [t.cuda().requires_grad_(True) for t in (mo, q, k, v)]
+    out, attn = ma.match_attention_autograd(*leaves, H, W, r, hd ** -0.5)
+    ((out * g_out.cuda()).sum() + (attn * g_attn.cuda()).sum()).backward()
+    for leaf, ref, key in zip(leaves, want, ("d_max_offset", "d_q", "d_k", "d_v")):
+        assert _rel(leaf.grad, ref) < 1e-4, key

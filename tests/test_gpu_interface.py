@@ -88,8 +88,8 @@ def test_bad_arguments_raise_and_leave_the_device_usable(case):
         match_attention(mo, q.transpose(0, 1).contiguous().transpose(0, 1), k, v, H, W, 1, 0.25)
     with pytest.raises(TypeError):         # mixed dtypes
         match_attention(mo.float(), q, k, v, H, W, 1, 0.25)
-    with pytest.raises(NotImplementedError):
-        launch(mo, q, k, v, torch.empty_like(q), None, H, W, (1, 1), "dot_product", 1.0)
+    with pytest.raises(NotImplementedError):   # a scoring function that does not exist
+        launch(mo, q, k, v, torch.empty_like(q), None, H, W, (1, 1), "l2_norm", 1.0)
     with pytest.raises(RuntimeError):      # rx != ry is rejected by the library
         launch(mo, q, k, v, torch.empty_like(q), None, H, W, (1, 2), "l1_norm", 1.0)
     with pytest.raises(ValueError):        # attn_num inconsistent with win_r
