@@ -19,7 +19,7 @@ split of one very large pair (`band`).
 `--impl reference` times the reference's own CPU implementation of the path (the
 unmodified copy under oracle/_ref/, else the C restatement) on the host cores,
 on a bounded sample of the same workload.  `--mode` selects the other
-measurements (model, model_ops, band, upsample, volume, backward).
+measurements (model, model_pairs, model_ops, band, upsample, volume, backward).
 """
 from __future__ import annotations
 
@@ -660,6 +660,122 @@ def measure_model(args, compile_ours, compile_reference, steps=None):
     return line
 
 
+def run_model_pairs_mode(args, rank, local_rank, world):
+    """BASELINE.json configs[3]: a fixed batch of image pairs (8 by default) through the reference's model
+    with this library's kernels, the pairs dealt out to the GPUs (one process per GPU, weights replicated,
+    no collective on the data path: a barrier brackets the timed region).  A step is the whole batch; with N
+    GPUs each rank runs its share of the pairs one after the other (strong scaling over the fixed batch).
+    Arm: the fused forward captured once as a CUDA graph and replayed, inputs copied into the graph's input
+    buffers from device-resident images (`value`) or from pinned host memory with the up-sampled field read
+    back to the host (`e2e`).  Rank 0 prints one JSON line with pairs per second over all GPUs."""
+    import types
+    from oracle import ref_loader
+    Hi, Wi = args.model_size
+    metric = f"match{'flow' if args.model_flow else 'stereo'}_{args.model_variant}_{Hi}x{Wi}_pairs_per_s"
+    if not ref_loader.available():
+        if rank == 0:
+            print(json.dumps({"metric": metric, "unavailable": "the reference's Python code is not present under "
+                              "oracle/_ref/ (oracle/make_ref.py places it where a checkout exists)"}), flush=True)
+        return
+    import matchattention_b200 as ma
+    from matchattention_b200.dropin.fused_model import patch_reference_model
+    from _cases import make_stereo_pair
+    ref_loader.import_reference()
+    from models.match_stereo import MatchStereo
+    ma.install_dropin()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    torch.backends.cudnn.benchmark = True
+    dtype = {"f16": torch.float16, "f32": torch.float32, "bf16": torch.bfloat16}[args.model_dtype]
+    stereo = not args.model_flow
+    total = args.model_pairs
+    if total % world != 0:
+        raise SystemExit(f"--model-pairs {total} does not divide over {world} GPUs")
+    mine = [i for i in range(total) if i % world == rank]
+    host = [tuple(t.to(dtype).pin_memory() for t in make_stereo_pair(100 + i, Hi, Wi, args.model_max_disp)) for i in mine]
+    resident = [(a.to(dev), b.to(dev)) for a, b in host]
+    torch.manual_seed(21)
+    model = MatchStereo(types.SimpleNamespace(variant=args.model_variant, mat_impl="cuda")).eval().to(dev).to(dtype)
+    patch_reference_model(model)
+    s_left, s_right = torch.empty_like(resident[0][0]), torch.empty_like(resident[0][1])
+    s_left.copy_(resident[0][0]); s_right.copy_(resident[0][1])
+    side = torch.cuda.Stream()
+    with torch.inference_mode():
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                model(s_left, s_right, stereo=stereo)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                out = model(s_left, s_right, stereo=stereo)
+    torch.cuda.synchronize()
+    field = out["field_up"]
+    field_host = torch.empty(field.shape, dtype=field.dtype).pin_memory()
+
+    def step_resident():
+        for a, b in resident:
+            s_left.copy_(a, non_blocking=True)
+            s_right.copy_(b, non_blocking=True)
+            graph.replay()
+
+    def step_host():
+        for a, b in host:
+            s_left.copy_(a, non_blocking=True)
+            s_right.copy_(b, non_blocking=True)
+            graph.replay()
+            field_host.copy_(field, non_blocking=True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step, k):
+        for _ in range(max(1, min(args.warmup, 3))):
+            step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k):
+            step()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / k
+
+    k = max(2, min(args.steps, 5))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t0 = time.perf_counter()
+    with torch.inference_mode():
+        ms_res = timed(step_resident, k)
+        t1 = time.perf_counter()
+        ms_host = timed(step_host, k)
+    sampler.stop()
+    if rank == 0:
+        h2d = sum(a.numel() * a.element_size() + b.numel() * b.element_size() for a, b in host)
+        d2h = field.numel() * field.element_size() * len(host)
+        print(json.dumps({
+            "metric": metric, "value": total / ms_res * 1e3, "unit": "pairs/s", "n_gpus": world, "steps": k,
+            "warmup": max(1, min(args.warmup, 3)), "ms_per_step": ms_res, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": args.model_dtype, "data": "synthetic",
+            "config": {"workload": f"Match{'Flow' if args.model_flow else 'Stereo'}-{args.model_variant} forward, batch of "
+                                   f"{total} pairs of {Hi}x{Wi}, dealt out over {world} GPU(s), random-init weights (seed 21)",
+                       "pairs_per_rank": len(mine), "ms_per_pair_per_gpu": ms_res / len(mine),
+                       "arm": "fused steps, one CUDA graph per forward"},
+            "e2e": {"value": total / ms_host * 1e3, "unit": "pairs/s", "ms_per_step": ms_host,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "bytes per rank; images from pinned host memory, up-sampled field read back"},
+            "clocks": sampler.summary(t0, t1)}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_model_mode(args):
     print(json.dumps(measure_model(args, args.model_compile, args.model_compile)), flush=True)
 
@@ -853,7 +969,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-shapes", action="store_true", help="skip the timing of the other configuration shapes")
     ap.add_argument("--no-model", action="store_true", help="skip the MatchStereo-T forward leg of the default line")
-    ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume", "backward"], default="pairs",
+    ap.add_argument("--mode", choices=["pairs", "band", "model", "model_ops", "upsample", "volume", "backward", "model_pairs"], default="pairs",
                     help="pairs: every GPU its own batch (default); band: one large pair split by query row bands; "
                          "model_ops: the 52 operator calls of one MatchStereo-T forward at 1536x1536")
     ap.add_argument("--no-band", action="store_true", help="with more than one GPU: skip the row-band measurement")
@@ -861,6 +977,7 @@ def main():
     ap.add_argument("--model-size", type=int, nargs=2, default=[1536, 1536], metavar=("H", "W"))
     ap.add_argument("--model-dtype", default="f16", choices=["f16", "bf16", "f32"])
     ap.add_argument("--model-max-disp", type=int, default=192)
+    ap.add_argument("--model-pairs", type=int, default=8, help="model_pairs mode: size of the batch dealt out to the GPUs")
     ap.add_argument("--model-flow", action="store_true", help="model mode: optical-flow forward (stereo=False)")
     ap.add_argument("--model-compile", action="store_true",
                     help="model mode: also time the model under torch.compile (minutes of compilation)")
@@ -891,6 +1008,9 @@ def main():
         return
     if args.mode == "model":
         run_model_mode(args)
+        return
+    if args.mode == "model_pairs":
+        run_model_pairs_mode(args, rank, local_rank, world)
         return
     if args.mode == "upsample":
         run_upsample_mode(args)
