@@ -271,9 +271,13 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
       resident_allgather  every rank holds its own rows of q/max_offset/K/V and keeps its rows of the outputs:
                           K/V rows all-gathered every step
       resident_halo       same, but only the rows a band can reach (|dy| <= 33 rows) move between neighbours
+                          (NCCL send / receive)
+      resident_halo_peer  same rows, pulled out of the neighbours' memory by peer copies over NVLink (the
+                          ranks' K/V buffers mapped into every process; no NCCL on the data path)
     Returns the dict that goes into the JSON line (on rank 0; None elsewhere)."""
     import matchattention_b200 as ma
-    from matchattention_b200.band import (band_match_attention, band_match_attention_resident, band_rows, halo_rows)
+    from matchattention_b200.band import (PeerBuffers, band_match_attention, band_match_attention_resident, band_rows,
+                                          halo_rows)
     B, H, W, h, hd, r, dtype = 2, 1024, 1024, 4, 32, 1, torch.float16
     N, C, M = H * W, h * hd, 16
     scale = hd ** -0.5
@@ -338,6 +342,24 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
                                                                     out=out_band, attn_out=attn_band, max_abs_dy=max_dy),
                               2 * B * ((lambda hr: (hr[1] - hr[0]) - (r1 - r0))(halo_rows(H, r0, r1, r, max_dy))) * W * C * esz),
         }
+        halo_bytes = variants["resident_halo"][1]
+        peers, peer_note = None, None
+        try:        # collective: every rank tries, and all of them drop the variant if one could not map
+            peers = PeerBuffers(B, N, C, dtype, dev)
+            for t, src in zip(peers.local, (k, v)):
+                t.fill_(float("nan"))
+                t[:, sl] = src[:, sl]
+        except Exception as exc:
+            peer_note = "peer mapping unavailable: " + str(exc).splitlines()[0][:200]
+        ok_all = torch.tensor([int(peers is not None)], device=dev)
+        dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+        if bool(ok_all.item()):
+            variants["resident_halo_peer"] = (lambda: band_match_attention_resident(
+                *bands, *peers.local, H, W, r, scale, out=out_band, attn_out=attn_band, max_abs_dy=max_dy, peers=peers),
+                halo_bytes)
+        else:
+            res["resident_halo_peer_note"] = peer_note or "peer mapping unavailable on another rank"
+            peers = None
         for name, (fn, recv_bytes) in variants.items():
             ms = timed(fn)
             res["variants"][name] = {"ms": ms, "speedup_vs_one_gpu": one_gpu / ms,
@@ -349,8 +371,14 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
             t[:, sl] = src[:, sl]
         band_match_attention_resident(*bands, *kv_full, H, W, r, scale, out=out_band, attn_out=attn_band,
                                       max_abs_dy=max_dy)
-        ok = torch.tensor([int(torch.equal(out_band, full_out[:, sl]) and torch.equal(attn_band, full_attn[:, sl]))],
-                          device=dev)
+        same = torch.equal(out_band, full_out[:, sl]) and torch.equal(attn_band, full_attn[:, sl])
+        if peers is not None:
+            out_band.zero_()
+            attn_band.zero_()
+            band_match_attention_resident(*bands, *peers.local, H, W, r, scale, out=out_band, attn_out=attn_band,
+                                          max_abs_dy=max_dy, peers=peers)
+            same = same and torch.equal(out_band, full_out[:, sl]) and torch.equal(attn_band, full_attn[:, sl])
+        ok = torch.tensor([int(same)], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         res["bands_bit_identical_to_one_gpu"] = bool(ok.item())
         best = min(res["variants"].items(), key=lambda kv_: kv_[1]["ms"])

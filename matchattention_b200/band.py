@@ -18,7 +18,9 @@ Two forms:
 * :func:`band_match_attention_resident` -- every rank already holds ITS rows of q, max_offset, K and
   V (the state of a pipeline whose producers are band-parallel too) and keeps its rows of the
   outputs.  K/V rows are exchanged with an all-gather, or, when the caller can bound how far a
-  centre lies from its query row, only the halo rows move between neighbouring ranks.
+  centre lies from its query row, only the halo rows move between neighbouring ranks: through NCCL
+  send / receive, or -- with :class:`PeerBuffers`, full-size K / V buffers that every rank maps into its
+  own address space -- pulled straight out of the neighbours' memory over NVLink by peer copies.
 
 :func:`band_check` is the CPU-side handshake to run before either form when the ranks' arguments
 come from different code paths: it fails on every rank if one rank reports an error or the
@@ -49,6 +51,16 @@ def halo_rows(H: int, r0: int, r1: int, r: int, max_abs_dy: float) -> Tuple[int,
     (floor + 2r + 2 taps), one more row covers the rounding of the bound."""
     reach = int(max_abs_dy) + 1
     return max(0, r0 - reach - r), min(H, r1 + reach + r + 2)
+
+
+def interior_rows(H: int, r0: int, r1: int, r: int, max_abs_dy: float) -> Tuple[int, int]:
+    """Query rows [i0, i1) of the band [r0, r1) whose windows stay inside the band's own key/value rows
+    under the same bound as halo_rows (their halo needs no other rank); i0 == i1 when there are none."""
+    reach = int(max_abs_dy) + 1
+    i0 = r0 if r0 == 0 else r0 + reach + r
+    i1 = r1 if r1 == H else r1 - (reach + r + 2)
+    i0, i1 = min(max(i0, r0), r1), min(max(i1, r0), r1)
+    return (i0, i1) if i1 > i0 else (r0, r0)
 
 
 def _default_op(mo, q, k, v, H, W, r, scale, r0, r1, need_attn):
@@ -242,10 +254,106 @@ def _exchange_rows(fulls: List[torch.Tensor], H: int, W: int, r: int, world: int
     _p2p(ops)
 
 
+class PeerBuffers:
+    """Full-size key / value buffers [B, H*W, C] of every rank, each mapped into every process of the group
+    (CUDA peer access over NVLink / NVSwitch through torch's symmetric memory; plain loads and copies, no
+    multicast object is created).  Construct it once, collectively, on every rank; a rank's producer writes
+    its own rows into ``local[0]`` (K) and ``local[1]`` (V) and passes them as k and v to
+    :func:`band_match_attention_resident` together with ``peers=this``."""
+
+    def __init__(self, B: int, N: int, C: int, dtype: torch.dtype, device: torch.device, group=None, count: int = 2):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # peer copies only
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.shape, self.dtype = (B, N, C), dtype
+        self.local, self._handles = [], []
+        for _ in range(count):
+            t = symm.empty(B, N, C, dtype=dtype, device=device)
+            self._handles.append(symm.rendezvous(t, self.group))
+            self.local.append(t)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.stream = torch.cuda.Stream(device=device)      # the pulls run here, beside the interior rows
+
+    def remote(self, index: int, rank: int) -> torch.Tensor:
+        """Rank `rank`'s buffer number `index`, as a tensor of this process."""
+        return self._handles[index].get_buffer(rank, self.shape, self.dtype)
+
+    def meet(self) -> None:
+        """Stream-ordered meeting of the ranks (a one-word all-reduce): when it has run on this rank's
+        stream, everything every rank had enqueued before its own call has run."""
+        dist.all_reduce(self._flag, group=self.group)
+
+
+def _pull_halo_rows(peers: PeerBuffers, H: int, W: int, r: int, world: int, rank: int, max_abs_dy: float,
+                    pulled_event: Optional[torch.cuda.Event] = None) -> int:
+    """Copy the rows this rank's band can reach out of the neighbouring ranks' buffers into its own
+    (one device-to-device peer copy per tensor, item and neighbour; the rows of an item are contiguous),
+    on the current stream.  `pulled_event` is recorded when this rank's copies are enqueued, before the
+    second meeting.  Returns the number of bytes pulled."""
+    r0, r1 = band_rows(H, world, rank)
+    g0, g1 = halo_rows(H, r0, r1, r, max_abs_dy)
+    pulled = 0
+    peers.meet()                                    # the neighbours' rows are in place
+    for p in range(world):
+        if p == rank:
+            continue
+        p0, p1 = band_rows(H, world, p)
+        lo, hi = max(g0, p0), min(g1, p1)
+        if hi <= lo:
+            continue
+        for index, mine in enumerate(peers.local):
+            theirs = peers.remote(index, p)
+            for b in range(mine.size(0)):
+                mine[b, lo * W:hi * W].copy_(theirs[b, lo * W:hi * W], non_blocking=True)
+                pulled += (hi - lo) * W * mine.size(2) * mine.element_size()
+    if pulled_event is not None:
+        pulled_event.record()
+    peers.meet()                                    # every pull is done: producers may write their rows again
+    return pulled
+
+
+def _peer_band_call(peers: PeerBuffers, mo_band, q_band, H, W, r, scale, world, rank, max_abs_dy, need_attn, out, attn_out):
+    """The band with its halo pulled by peer copies on a second stream while the interior rows (whose windows
+    stay inside the band's own rows) are computed; the edge rows follow the copies.  Launches are per
+    item and per part: an item's rows of a part are contiguous."""
+    from .ops import match_attention
+    B, _, C = q_band.shape
+    h = mo_band.size(2)
+    r0, r1 = band_rows(H, world, rank)
+    k, v = peers.local
+    if out is None:
+        out = torch.empty_like(q_band)
+    if need_attn and attn_out is None:
+        attn_out = q_band.new_empty(B, (r1 - r0) * W, h, (2 * r + 2) ** 2)
+    main = torch.cuda.current_stream(q_band.device)
+    pulled = torch.cuda.Event()
+    peers.stream.wait_stream(main)                  # this rank's producer has written its rows
+    with torch.cuda.stream(peers.stream):
+        _pull_halo_rows(peers, H, W, r, world, rank, max_abs_dy, pulled)
+
+    def part(a, b):
+        if b <= a:
+            return
+        sl = slice((a - r0) * W, (b - r0) * W)
+        for i in range(B):
+            match_attention(mo_band[i:i + 1, sl], q_band[i:i + 1, sl], k[i:i + 1], v[i:i + 1], H, W, r, scale,
+                            need_attn=need_attn, q_row_begin=a, q_row_end=b, out=out[i:i + 1, sl],
+                            attn_out=attn_out[i:i + 1, sl] if need_attn else None)
+
+    i0, i1 = interior_rows(H, r0, r1, r, max_abs_dy)
+    part(i0, i1)
+    main.wait_event(pulled)
+    part(r0, i0)
+    part(i1, r1)
+    main.wait_stream(peers.stream)                  # the second meeting: nobody still reads this rank's rows
+    return out, (attn_out if need_attn else None)
+
+
 def band_match_attention_resident(mo_band: torch.Tensor, q_band: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                   H: int, W: int, r: int, scale: float, *, group=None, need_attn: bool = True,
                                   op: Optional[Callable] = None, kv_full=None, max_abs_dy: Optional[float] = None,
-                                  out=None, attn_out=None):
+                                  out=None, attn_out=None, peers: Optional["PeerBuffers"] = None):
     """One MatchAttention call over row bands that already live on their ranks.
 
     Every rank passes ITS rows [r0, r1) = band_rows(H, world, rank) of max_offset [B,rows*W,h,2] and of
@@ -259,6 +367,8 @@ def band_match_attention_resident(mo_band: torch.Tensor, q_band: torch.Tensor, k
     The missing rows arrive by an all-gather of the bands or -- with `max_abs_dy`, the caller's bound in
     rows on |centre_y - query row| -- only the halo rows each band can reach travel between neighbouring
     ranks; rows outside stay untouched and are never read.  The kernel follows on the rank's own stream.
+    With `peers` (and `max_abs_dy`), k and v must be ``peers.local`` and the halo rows are pulled out of
+    the neighbours' memory by peer copies instead of NCCL send / receive.
     """
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     op = op or _default_op
@@ -276,7 +386,15 @@ def band_match_attention_resident(mo_band: torch.Tensor, q_band: torch.Tensor, k
     def peer(p):
         return dist.get_global_rank(group, p) if group is not None else p
 
-    _exchange_rows(fulls, H, W, r, world, rank, group, max_abs_dy, peer)
+    if peers is not None and world > 1:
+        if max_abs_dy is None or k is not peers.local[0] or v is not peers.local[1]:
+            raise ValueError("peers: pass max_abs_dy, and peers.local[0] / peers.local[1] as k / v")
+        if op is _default_op and r1 > r0:
+            return _peer_band_call(peers, mo_band, q_band, H, W, r, scale, world, rank, max_abs_dy, need_attn,
+                                   out, attn_out)
+        _pull_halo_rows(peers, H, W, r, world, rank, max_abs_dy)
+    else:
+        _exchange_rows(fulls, H, W, r, world, rank, group, max_abs_dy, peer)
     if r1 == r0:
         return None, None
     if op is _default_op:

@@ -36,6 +36,21 @@ def test_halo_rows_cover_the_window():
         assert h0 <= lowest and h1 > highest
 
 
+def test_interior_rows_are_exactly_the_rows_that_need_no_halo():
+    from matchattention_b200.band import band_rows, halo_rows, interior_rows
+    for H in (16, 64, 100, 1024):
+        for world in (1, 2, 3, 4, 8):
+            for r in (0, 1, 2):
+                for dy in (0.0, 0.4, 3.0, 33.0, 200.0):
+                    for rank in range(world):
+                        r0, r1 = band_rows(H, world, rank)
+                        i0, i1 = interior_rows(H, r0, r1, r, dy)
+                        assert r0 <= i0 <= i1 <= r1
+                        for y in range(r0, r1):
+                            g0, g1 = halo_rows(H, y, y + 1, r, dy)
+                            assert (i0 <= y < i1) == (g0 >= r0 and g1 <= r1), (H, world, r, dy, rank, y)
+
+
 def _worker(rank, world, port, H, W, results, max_abs_dy=None):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
