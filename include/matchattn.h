@@ -329,6 +329,16 @@ MATCHATTN_API int matchattn_flow_init(const void *correlation, void *prob, void 
  * "generic", ...) or NULL if they are rejected.  Launches nothing. */
 MATCHATTN_API const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int pointers_32B_aligned);
 
+/*
+ * Row-band helper (no counterpart in the reference, which has no multi-GPU code): enqueue `count`
+ * device-to-device copies dst[i] <- src[i] of bytes[i] bytes on `cuda_stream`, one cudaMemcpyAsync each.
+ * Source and destination may live on different GPUs of the box when the caller has mapped the peer's
+ * memory into this process (the halo rows of K / V that a band pulls out of its neighbours' buffers,
+ * matchattention_b200/band.py).  Nothing is allocated; the arrays are host memory read before return.
+ */
+MATCHATTN_API int matchattn_copy_blocks(void *const *dst, const void *const *src, const size_t *bytes, int count,
+                                        void *cuda_stream);
+
 /* version of this ABI: major * 100 + minor */
 MATCHATTN_API int matchattn_version(void);
 

@@ -16,7 +16,7 @@ EXPORTS = ("matchattn_fused_forward", "matchattn_fused_forward_ex", "matchattn_f
            "matchattn_fused_forward_static", "matchattn_fused_forward_glue", "matchattn_fused_forward_checked",
            "matchattn_fused_backward", "matchattn_upsample_field",
            "matchattn_stereo_volume", "matchattn_consistency_mask", "matchattn_local_disparity",
-           "matchattn_flow_init", "matchattn_flow_init_scratch_bytes",
+           "matchattn_flow_init", "matchattn_flow_init_scratch_bytes", "matchattn_copy_blocks",
            "matchattn_workspace_bytes", "matchattn_describe_dispatch", "matchattn_version", "matchattn_strerror")
 
 F32, F16, BF16 = 0, 1, 2
@@ -65,6 +65,8 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_workspace_bytes.argtypes = [_i] * 9
     lib.matchattn_describe_dispatch.restype = ctypes.c_char_p
     lib.matchattn_describe_dispatch.argtypes = [_i] * 5
+    lib.matchattn_copy_blocks.restype = _i
+    lib.matchattn_copy_blocks.argtypes = [ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_size_t), _i, _vp]
     lib.matchattn_version.restype = _i
     lib.matchattn_version.argtypes = []
     lib.matchattn_strerror.restype = ctypes.c_char_p

@@ -274,6 +274,7 @@ class PeerBuffers:
             self.local.append(t)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         self.stream = torch.cuda.Stream(device=device)      # the pulls run here, beside the interior rows
+        self._plans = {}
 
     def remote(self, index: int, rank: int) -> torch.Tensor:
         """Rank `rank`'s buffer number `index`, as a tensor of this process."""
@@ -285,67 +286,107 @@ class PeerBuffers:
         dist.all_reduce(self._flag, group=self.group)
 
 
+def _halo_copy_plan(peers: PeerBuffers, H: int, W: int, r: int, world: int, rank: int, max_abs_dy: float):
+    """The device-to-device copies that bring the rows this rank's band can reach out of the neighbouring
+    ranks' buffers into its own: one per tensor, item and neighbour (the rows of an item are contiguous).
+    Built once per geometry (the mapped buffers do not move) as the argument arrays of
+    matchattn_copy_blocks; returns (dst, src, nbytes, count, total_bytes)."""
+    import ctypes
+    key = (H, W, r, world, rank, float(max_abs_dy))
+    plan = peers._plans.get(key)
+    if plan is None:
+        r0, r1 = band_rows(H, world, rank)
+        g0, g1 = halo_rows(H, r0, r1, r, max_abs_dy)
+        B, N, C = peers.shape
+        esz = peers.local[0].element_size()
+        dst, src, nbytes = [], [], []
+        for p in range(world):
+            if p == rank:
+                continue
+            p0, p1 = band_rows(H, world, p)
+            lo, hi = max(g0, p0), min(g1, p1)
+            if hi <= lo:
+                continue
+            for index, mine in enumerate(peers.local):
+                theirs = peers.remote(index, p)
+                for b in range(B):
+                    off = (b * N + lo * W) * C * esz
+                    dst.append(mine.data_ptr() + off)
+                    src.append(theirs.data_ptr() + off)
+                    nbytes.append((hi - lo) * W * C * esz)
+        n = len(dst)
+        plan = ((ctypes.c_void_p * n)(*dst), (ctypes.c_void_p * n)(*src), (ctypes.c_size_t * n)(*nbytes), n, sum(nbytes))
+        peers._plans[key] = plan
+    return plan
+
+
 def _pull_halo_rows(peers: PeerBuffers, H: int, W: int, r: int, world: int, rank: int, max_abs_dy: float,
                     pulled_event: Optional[torch.cuda.Event] = None) -> int:
-    """Copy the rows this rank's band can reach out of the neighbouring ranks' buffers into its own
-    (one device-to-device peer copy per tensor, item and neighbour; the rows of an item are contiguous),
-    on the current stream.  `pulled_event` is recorded when this rank's copies are enqueued, before the
-    second meeting.  Returns the number of bytes pulled."""
-    r0, r1 = band_rows(H, world, rank)
-    g0, g1 = halo_rows(H, r0, r1, r, max_abs_dy)
-    pulled = 0
-    peers.meet()                                    # the neighbours' rows are in place
-    for p in range(world):
-        if p == rank:
-            continue
-        p0, p1 = band_rows(H, world, p)
-        lo, hi = max(g0, p0), min(g1, p1)
-        if hi <= lo:
-            continue
-        for index, mine in enumerate(peers.local):
-            theirs = peers.remote(index, p)
-            for b in range(mine.size(0)):
-                mine[b, lo * W:hi * W].copy_(theirs[b, lo * W:hi * W], non_blocking=True)
-                pulled += (hi - lo) * W * mine.size(2) * mine.element_size()
+    """Pull the halo rows on the current stream, between two meetings of the ranks: the first says every
+    rank's own rows are in place, the second that every pull is done (producers may write their rows
+    again).  `pulled_event` is recorded between this rank's copies and the second meeting.  Returns the
+    number of bytes pulled."""
+    from . import _lib
+    dst, src, nbytes, count, total = _halo_copy_plan(peers, H, W, r, world, rank, max_abs_dy)
+    peers.meet()
+    with torch.cuda.device(peers.local[0].device):
+        _lib.check(_lib.lib.matchattn_copy_blocks(dst, src, nbytes, count, torch.cuda.current_stream().cuda_stream))
     if pulled_event is not None:
         pulled_event.record()
-    peers.meet()                                    # every pull is done: producers may write their rows again
-    return pulled
+    peers.meet()
+    return total
 
 
 def _peer_band_call(peers: PeerBuffers, mo_band, q_band, H, W, r, scale, world, rank, max_abs_dy, need_attn, out, attn_out):
     """The band with its halo pulled by peer copies on a second stream while the interior rows (whose windows
     stay inside the band's own rows) are computed; the edge rows follow the copies.  Launches are per
-    item and per part: an item's rows of a part are contiguous."""
-    from .ops import match_attention
-    B, _, C = q_band.shape
+    item and per part (an item's rows of a part are contiguous), straight through the C ABI."""
+    from . import _lib
+    from .ops import _DTYPE_CODE
+    B, Nq, C = q_band.shape
     h = mo_band.size(2)
     r0, r1 = band_rows(H, world, rank)
     k, v = peers.local
+    M = (2 * r + 2) ** 2
     if out is None:
         out = torch.empty_like(q_band)
     if need_attn and attn_out is None:
-        attn_out = q_band.new_empty(B, (r1 - r0) * W, h, (2 * r + 2) ** 2)
+        attn_out = q_band.new_empty(B, Nq, h, M)
+    for name, t, shape in (("max_offset", mo_band, (B, Nq, h, 2)), ("q", q_band, (B, Nq, C)), ("out", out, (B, Nq, C)),
+                           ("attn_out", attn_out if need_attn else None, (B, Nq, h, M))):
+        if t is None:
+            continue
+        if (tuple(t.shape) != shape or t.dtype != k.dtype or t.device != k.device or not t.is_contiguous()):
+            raise ValueError(f"{name}: expected a contiguous {shape} tensor of the buffers' dtype on their device")
+    if Nq != (r1 - r0) * W or C % h != 0 or tuple(k.shape) != (B, H * W, C):
+        raise ValueError("band tensors do not match the geometry of the peer buffers")
+    esz, code = q_band.element_size(), _DTYPE_CODE[q_band.dtype]
     main = torch.cuda.current_stream(q_band.device)
     pulled = torch.cuda.Event()
     peers.stream.wait_stream(main)                  # this rank's producer has written its rows
     with torch.cuda.stream(peers.stream):
         _pull_halo_rows(peers, H, W, r, world, rank, max_abs_dy, pulled)
 
+    fwd, stream_ptr = _lib.lib.matchattn_fused_forward, main.cuda_stream
+    mo_p, q_p, k_p, v_p, out_p = (t.data_ptr() for t in (mo_band, q_band, k, v, out))
+    attn_p = attn_out.data_ptr() if need_attn else None
+
     def part(a, b):
         if b <= a:
             return
-        sl = slice((a - r0) * W, (b - r0) * W)
         for i in range(B):
-            match_attention(mo_band[i:i + 1, sl], q_band[i:i + 1, sl], k[i:i + 1], v[i:i + 1], H, W, r, scale,
-                            need_attn=need_attn, q_row_begin=a, q_row_end=b, out=out[i:i + 1, sl],
-                            attn_out=attn_out[i:i + 1, sl] if need_attn else None)
+            first = i * Nq + (a - r0) * W                        # first query of the part within the band tensors
+            _lib.check(fwd(mo_p + first * h * 2 * esz, q_p + first * C * esz, k_p + i * H * W * C * esz,
+                           v_p + i * H * W * C * esz, out_p + first * C * esz,
+                           attn_p + first * h * M * esz if need_attn else None,
+                           1, H, W, h, C // h, r, r, code, _lib.L1_NORM, float(scale), a, b, stream_ptr))
 
     i0, i1 = interior_rows(H, r0, r1, r, max_abs_dy)
-    part(i0, i1)
-    main.wait_event(pulled)
-    part(r0, i0)
-    part(i1, r1)
+    with torch.cuda.device(q_band.device):
+        part(i0, i1)
+        main.wait_event(pulled)
+        part(r0, i0)
+        part(i1, r1)
     main.wait_stream(peers.stream)                  # the second meeting: nobody still reads this rank's rows
     return out, (attn_out if need_attn else None)
 

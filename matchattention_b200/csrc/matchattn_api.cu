@@ -604,7 +604,20 @@ const char *matchattn_describe_dispatch(int h, int hd, int r, int dtype, int poi
     return text;
 }
 
-int matchattn_version(void) { return 101; }
+int matchattn_copy_blocks(void *const *dst, const void *const *src, const size_t *bytes, int count, void *cuda_stream)
+{
+    if (count < 0 || (count > 0 && (!dst || !src || !bytes))) return MATCHATTN_ERR_NULL;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    for (int i = 0; i < count; ++i) {
+        if (bytes[i] == 0) continue;
+        if (!dst[i] || !src[i]) return MATCHATTN_ERR_NULL;
+        const cudaError_t err = cudaMemcpyAsync(dst[i], src[i], bytes[i], cudaMemcpyDefault, stream);
+        if (err != cudaSuccess) return MATCHATTN_ERR_CUDA + static_cast<int>(err);
+    }
+    return MATCHATTN_OK;
+}
+
+int matchattn_version(void) { return 102; }
 
 const char *matchattn_strerror(int status)
 {
