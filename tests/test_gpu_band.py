@@ -1,4 +1,4 @@
-"""GPU test of the row-band path over NCCL: needs at least two GPUs (skipped otherwise).
+"""GPU test of the row-band path over NCCL and over peer copies: needs at least two GPUs (skipped otherwise).
 Each rank is its own process on its own GPU; the result on rank 0 must equal the
 single-GPU result bit for bit and match the oracle."""
 import os
@@ -51,6 +51,21 @@ def _worker(rank, world, port, results):
                                                    0.2, max_abs_dy=max_dy)
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(ob, one_out[:, sl])) and bool(torch.equal(ab, one_attn[:, sl]))
+        # the same halo rows pulled out of the neighbours' memory by peer copies (buffers mapped into every
+        # process), twice (the copy plan is reused), with and without the attention weights
+        from matchattention_b200.band import PeerBuffers
+        peers = PeerBuffers(B, H2 * W, h * hd, torch.float16, dev)
+        for t, src in zip(peers.local, (k, v)):
+            t.fill_(float("nan"))
+            t[:, sl] = src[:, sl]
+        torch.cuda.synchronize()
+        dist.barrier()
+        for need_attn in (True, False, True):
+            ob, ab = band_match_attention_resident(mo[:, sl].contiguous(), q[:, sl].contiguous(), *peers.local, H2, W, r,
+                                                   0.2, max_abs_dy=4.0, peers=peers, need_attn=need_attn)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(ob, one_out[:, sl])) and (ab is None or bool(torch.equal(ab, one_attn[:, sl])))
+            ok = ok and (ab is None) == (not need_attn)
         results.put(("resident", rank, ok))
         dist.barrier()
     finally:
