@@ -354,6 +354,7 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
         ok_all = torch.tensor([int(peers is not None)], device=dev)
         dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
         if bool(ok_all.item()):
+            res["peer_buffers_multicast_bound"] = peers.multicast_bound
             variants["resident_halo_peer"] = (lambda: band_match_attention_resident(
                 *bands, *peers.local, H, W, r, scale, out=out_band, attn_out=attn_band, max_abs_dy=max_dy, peers=peers),
                 halo_bytes)

@@ -276,6 +276,12 @@ class PeerBuffers:
         self.stream = torch.cuda.Stream(device=device)      # the pulls run here, beside the interior rows
         self._plans = {}
 
+    @property
+    def multicast_bound(self) -> bool:
+        """True if the mapping also created an NVLink multicast address (not used by this module; it is
+        asked not to through TORCH_SYMM_MEM_DISABLE_MULTICAST)."""
+        return any(int(getattr(hdl, "multicast_ptr", 0) or 0) != 0 for hdl in self._handles)
+
     def remote(self, index: int, rank: int) -> torch.Tensor:
         """Rank `rank`'s buffer number `index`, as a tensor of this process."""
         return self._handles[index].get_buffer(rank, self.shape, self.dtype)
