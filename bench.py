@@ -272,8 +272,9 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
                           K/V rows all-gathered every step
       resident_halo       same, but only the rows a band can reach (|dy| <= 33 rows) move between neighbours
                           (NCCL send / receive)
-      resident_halo_peer  same rows, pulled out of the neighbours' memory by peer copies over NVLink (the
-                          ranks' K/V buffers mapped into every process; no NCCL on the data path)
+      resident_halo_peer  same rows, pulled out of the neighbours' memory over NVLink (the ranks' K/V buffers
+                          mapped into every process; no NCCL on the data path) by one cudaMemcpyAsync per
+                          block (copy engines), or (`_copy_kernel`) by a copy kernel with plain peer loads
     Returns the dict that goes into the JSON line (on rank 0; None elsewhere)."""
     import matchattention_b200 as ma
     from matchattention_b200.band import (PeerBuffers, band_match_attention, band_match_attention_resident, band_rows,
@@ -355,9 +356,14 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
         dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
         if bool(ok_all.item()):
             res["peer_buffers_multicast_bound"] = peers.multicast_bound
-            variants["resident_halo_peer"] = (lambda: band_match_attention_resident(
-                *bands, *peers.local, H, W, r, scale, out=out_band, attn_out=attn_band, max_abs_dy=max_dy, peers=peers),
-                halo_bytes)
+            def peer_call(by_kernel):
+                def call():
+                    peers.copy_by_kernel = by_kernel
+                    return band_match_attention_resident(*bands, *peers.local, H, W, r, scale, out=out_band,
+                                                         attn_out=attn_band, max_abs_dy=max_dy, peers=peers)
+                return call
+            variants["resident_halo_peer"] = (peer_call(False), halo_bytes)
+            variants["resident_halo_peer_copy_kernel"] = (peer_call(True), halo_bytes)
         else:
             res["resident_halo_peer_note"] = peer_note or "peer mapping unavailable on another rank"
             peers = None

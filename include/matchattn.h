@@ -331,13 +331,16 @@ MATCHATTN_API const char *matchattn_describe_dispatch(int h, int hd, int r, int 
 
 /*
  * Row-band helper (no counterpart in the reference, which has no multi-GPU code): enqueue `count`
- * device-to-device copies dst[i] <- src[i] of bytes[i] bytes on `cuda_stream`, one cudaMemcpyAsync each.
- * Source and destination may live on different GPUs of the box when the caller has mapped the peer's
- * memory into this process (the halo rows of K / V that a band pulls out of its neighbours' buffers,
- * matchattention_b200/band.py).  Nothing is allocated; the arrays are host memory read before return.
+ * device-to-device copies dst[i] <- src[i] of bytes[i] bytes on `cuda_stream`.  Source and destination
+ * may live on different GPUs of the box when the caller has mapped the peer's memory into this process
+ * (the halo rows of K / V that a band pulls out of its neighbours' buffers, matchattention_b200/band.py).
+ * use_kernel == 0: one cudaMemcpyAsync per block (copy engines).  use_kernel != 0: one kernel launch per
+ * sixteen blocks reads the sources with plain 16-byte loads (over NVLink when they are a peer's) and
+ * stores locally; blocks whose addresses or sizes are not multiples of 16 bytes still go through
+ * cudaMemcpyAsync.  Nothing is allocated; the arrays are host memory read before return.
  */
 MATCHATTN_API int matchattn_copy_blocks(void *const *dst, const void *const *src, const size_t *bytes, int count,
-                                        void *cuda_stream);
+                                        int use_kernel, void *cuda_stream);
 
 /* version of this ABI: major * 100 + minor */
 MATCHATTN_API int matchattn_version(void);

@@ -66,7 +66,7 @@ def _load() -> ctypes.CDLL:
     lib.matchattn_describe_dispatch.restype = ctypes.c_char_p
     lib.matchattn_describe_dispatch.argtypes = [_i] * 5
     lib.matchattn_copy_blocks.restype = _i
-    lib.matchattn_copy_blocks.argtypes = [ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_size_t), _i, _vp]
+    lib.matchattn_copy_blocks.argtypes = [ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_size_t), _i, _i, _vp]
     lib.matchattn_version.restype = _i
     lib.matchattn_version.argtypes = []
     lib.matchattn_strerror.restype = ctypes.c_char_p

@@ -275,6 +275,9 @@ class PeerBuffers:
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         self.stream = torch.cuda.Stream(device=device)      # the pulls run here, beside the interior rows
         self._plans = {}
+        # halo rows by the copy engines (default: the SMs stay with the interior rows; measured as fast or
+        # faster at 2, 4 and 8 GPUs) or by a copy kernel with plain peer loads
+        self.copy_by_kernel = False
 
     @property
     def multicast_bound(self) -> bool:
@@ -336,7 +339,8 @@ def _pull_halo_rows(peers: PeerBuffers, H: int, W: int, r: int, world: int, rank
     dst, src, nbytes, count, total = _halo_copy_plan(peers, H, W, r, world, rank, max_abs_dy)
     peers.meet()
     with torch.cuda.device(peers.local[0].device):
-        _lib.check(_lib.lib.matchattn_copy_blocks(dst, src, nbytes, count, torch.cuda.current_stream().cuda_stream))
+        _lib.check(_lib.lib.matchattn_copy_blocks(dst, src, nbytes, count, int(peers.copy_by_kernel),
+                                                  torch.cuda.current_stream().cuda_stream))
     if pulled_event is not None:
         pulled_event.record()
     peers.meet()
