@@ -67,6 +67,16 @@ def _worker(rank, world, port, results):
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(ob, one_out[:, sl])) and (ab is None or bool(torch.equal(ab, one_attn[:, sl])))
             ok = ok and (ab is None) == (not need_attn)
+        # the producers write new rows and the call follows at once on the same stream: the first meeting
+        # of the ranks must order every rank's writes before the neighbours' pulls
+        for step in range(3):
+            k2, v2 = k * (step + 2), v + (step + 1)
+            want_out, want_attn = match_attention(mo, q, k2, v2, H2, W, r, 0.2)
+            peers.local[0][:, sl], peers.local[1][:, sl] = k2[:, sl], v2[:, sl]
+            ob, ab = band_match_attention_resident(mo[:, sl].contiguous(), q[:, sl].contiguous(), *peers.local, H2, W, r,
+                                                   0.2, max_abs_dy=4.0, peers=peers)
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(ob, want_out[:, sl])) and bool(torch.equal(ab, want_attn[:, sl]))
         results.put(("resident", rank, ok))
         dist.barrier()
     finally:
