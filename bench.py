@@ -273,8 +273,9 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
       resident_halo       same, but only the rows a band can reach (|dy| <= 33 rows) move between neighbours
                           (NCCL send / receive)
       resident_halo_peer  same rows, pulled out of the neighbours' memory over NVLink (the ranks' K/V buffers
-                          mapped into every process; no NCCL on the data path) by one cudaMemcpyAsync per
-                          block (copy engines), or (`_copy_kernel`) by a copy kernel with plain peer loads
+                          mapped into every process; no NCCL on the data path): `_copy_engines` by one
+                          cudaMemcpyAsync per block, `_copy_kernel` by a copy kernel with plain peer loads,
+                          no suffix: the library chooses between the two by the size of the band's interior
     Returns the dict that goes into the JSON line (on rank 0; None elsewhere)."""
     import matchattention_b200 as ma
     from matchattention_b200.band import (PeerBuffers, band_match_attention, band_match_attention_resident, band_rows,
@@ -362,8 +363,9 @@ def measure_band(rank, world, dev, dist, steps=10, warmup=3):
                     return band_match_attention_resident(*bands, *peers.local, H, W, r, scale, out=out_band,
                                                          attn_out=attn_band, max_abs_dy=max_dy, peers=peers)
                 return call
-            variants["resident_halo_peer"] = (peer_call(False), halo_bytes)
+            variants["resident_halo_peer_copy_engines"] = (peer_call(False), halo_bytes)
             variants["resident_halo_peer_copy_kernel"] = (peer_call(True), halo_bytes)
+            variants["resident_halo_peer"] = (peer_call(None), halo_bytes)        # the library's own choice
         else:
             res["resident_halo_peer_note"] = peer_note or "peer mapping unavailable on another rank"
             peers = None

@@ -273,11 +273,26 @@ class PeerBuffers:
             self._handles.append(symm.rendezvous(t, self.group))
             self.local.append(t)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
-        self.stream = torch.cuda.Stream(device=device)      # the pulls run here, beside the interior rows
+        # The pulls and the meetings run beside the band's kernels, which fill every SM: on streams of
+        # ordinary priority the one-block all-reduce of a meeting is dispatched only after the blocks of
+        # a kernel launched before it (measured: 0.3 ms per meeting at 2 GPUs).  Hence a high-priority
+        # stream here and, when the group is the whole job, an NCCL communicator of its own for the
+        # meetings whose internal stream has high priority too.
+        self.stream = torch.cuda.Stream(device=device, priority=-1)
+        self._meet_group = self.group
+        if self.group is dist.group.WORLD and dist.get_backend(self.group) == "nccl":
+            try:
+                options = dist.ProcessGroupNCCL.Options()
+                options.is_high_priority_stream = True
+                self._meet_group = dist.new_group(backend="nccl", pg_options=options)
+            except Exception:
+                self._meet_group = self.group
         self._plans = {}
-        # halo rows by the copy engines (default: the SMs stay with the interior rows; measured as fast or
-        # faster at 2, 4 and 8 GPUs) or by a copy kernel with plain peer loads
-        self.copy_by_kernel = False
+        # Halo rows by the copy engines (False: the SMs stay with the interior rows) or by a copy kernel with
+        # plain peer loads (True).  None chooses per call: the kernel when the band's interior is smaller
+        # than its edges (measured at 8 GPUs, 56 interior rows of 128: 0.32 against 0.36 ms), the copy
+        # engines otherwise (2 GPUs, 440 of 512: 0.68 against 0.69 ms).
+        self.copy_by_kernel = None
 
     @property
     def multicast_bound(self) -> bool:
@@ -292,7 +307,7 @@ class PeerBuffers:
     def meet(self) -> None:
         """Stream-ordered meeting of the ranks (a one-word all-reduce): when it has run on this rank's
         stream, everything every rank had enqueued before its own call has run."""
-        dist.all_reduce(self._flag, group=self.group)
+        dist.all_reduce(self._flag, group=self._meet_group)
 
 
 def _halo_copy_plan(peers: PeerBuffers, H: int, W: int, r: int, world: int, rank: int, max_abs_dy: float):
@@ -337,9 +352,14 @@ def _pull_halo_rows(peers: PeerBuffers, H: int, W: int, r: int, world: int, rank
     number of bytes pulled."""
     from . import _lib
     dst, src, nbytes, count, total = _halo_copy_plan(peers, H, W, r, world, rank, max_abs_dy)
+    by_kernel = peers.copy_by_kernel
+    if by_kernel is None:
+        r0, r1 = band_rows(H, world, rank)
+        i0, i1 = interior_rows(H, r0, r1, r, max_abs_dy)
+        by_kernel = 2 * (i1 - i0) < (r1 - r0)
     peers.meet()
     with torch.cuda.device(peers.local[0].device):
-        _lib.check(_lib.lib.matchattn_copy_blocks(dst, src, nbytes, count, int(peers.copy_by_kernel),
+        _lib.check(_lib.lib.matchattn_copy_blocks(dst, src, nbytes, count, int(bool(by_kernel)),
                                                   torch.cuda.current_stream().cuda_stream))
     if pulled_event is not None:
         pulled_event.record()

@@ -60,7 +60,7 @@ def _worker(rank, world, port, results):
             t[:, sl] = src[:, sl]
         torch.cuda.synchronize()
         dist.barrier()
-        for need_attn, by_kernel in ((True, False), (False, True), (True, True)):
+        for need_attn, by_kernel in ((True, False), (False, True), (True, None)):
             peers.copy_by_kernel = by_kernel        # copy engines / copy kernel with plain peer loads
             ob, ab = band_match_attention_resident(mo[:, sl].contiguous(), q[:, sl].contiguous(), *peers.local, H2, W, r,
                                                    0.2, max_abs_dy=4.0, peers=peers, need_attn=need_attn)
