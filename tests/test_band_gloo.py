@@ -51,6 +51,42 @@ def test_interior_rows_are_exactly_the_rows_that_need_no_halo():
                             assert (i0 <= y < i1) == (g0 >= r0 and g1 <= r1), (H, world, r, dy, rank, y)
 
 
+def test_halo_copy_plan_moves_exactly_the_reachable_rows():
+    """The copy plan of the peer path (pointers and sizes handed to matchattn_copy_blocks), run here with
+    host tensors standing in for the mapped buffers of every rank and memmove for the device copies:
+    afterwards a rank holds its own rows and its halo rows of every tensor and item, and nothing else."""
+    import ctypes
+    import types
+    from matchattention_b200.band import _halo_copy_plan, band_rows, halo_rows
+    B, H, W, C, r = 2, 40, 3, 4, 1
+    for world, dy in ((2, 3.0), (4, 2.0), (5, 0.4), (3, 30.0)):
+        truth = [torch.arange(B * H * W * C, dtype=torch.float32).view(B, H * W, C) + 1000 * t for t in range(2)]
+        buffers = []                                  # buffers[rank][tensor]: own rows valid, the rest NaN
+        for rank in range(world):
+            r0, r1 = band_rows(H, world, rank)
+            mine = [torch.full_like(t, float("nan")) for t in truth]
+            for m, t in zip(mine, truth):
+                m[:, r0 * W:r1 * W] = t[:, r0 * W:r1 * W]
+            buffers.append(mine)
+        for rank in range(world):
+            fake = types.SimpleNamespace(shape=(B, H * W, C), local=buffers[rank], _plans={},
+                                         remote=lambda index, p: buffers[p][index])
+            dst, src, nbytes, count, total = _halo_copy_plan(fake, H, W, r, world, rank, dy)
+            for i in range(count):
+                ctypes.memmove(dst[i], src[i], nbytes[i])
+            assert total == sum(nbytes[i] for i in range(count))
+        for rank in range(world):
+            r0, r1 = band_rows(H, world, rank)
+            g0, g1 = halo_rows(H, r0, r1, r, dy)
+            for m, t in zip(buffers[rank], truth):
+                rows = m.view(B, H, W * C)
+                valid = ~torch.isnan(rows).any(dim=2)                       # [B, H]
+                want = torch.zeros(H, dtype=torch.bool)
+                want[g0:g1] = True
+                assert bool((valid == want).all()), (world, dy, rank)
+                assert torch.equal(m[:, g0 * W:g1 * W], t[:, g0 * W:g1 * W])
+
+
 def _worker(rank, world, port, H, W, results, max_abs_dy=None):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
