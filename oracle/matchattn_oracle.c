@@ -10,6 +10,11 @@
  * with golden vectors produced by executing the reference's own Python
  * functions (models/mat_pytorch_impl.py) on seeded inputs; the script that
  * made the vectors is tests/golden/make_golden.py.
+ * One exception, PARITY UNPINNED: the dot-product scoring (attn_type 1 of
+ * matchattn_oracle_forward_scored).  The reference has it only as an unused
+ * native kernel (models/src/match_former_fused_forward.cu:222-251), which cannot
+ * run without a GPU, and has no PyTorch form of it; its vectors come from the
+ * reference's functions with the one scoring line swapped for the product form.
  *
  * What is restated (reference file:line):
  *   - window origin  floor(max_offset)            models/attention_blocks.py:82
