@@ -52,6 +52,20 @@ def test_arguments_are_rejected_on_the_host():
         assert _lib.strerror(code) not in ("ok", "unknown status")
 
 
+def test_block_copy_arguments_are_checked_on_the_host():
+    """matchattn_copy_blocks: an empty list is fine, a negative count or a missing array or pointer is
+    refused before any CUDA call."""
+    from matchattention_b200 import _lib
+    f = _lib.lib.matchattn_copy_blocks
+    none = ctypes.POINTER(ctypes.c_void_p)()
+    assert f(none, none, ctypes.POINTER(ctypes.c_size_t)(), 0, 0, None) == 0
+    assert f(none, none, ctypes.POINTER(ctypes.c_size_t)(), -1, 0, None) == 1
+    assert f(none, none, ctypes.POINTER(ctypes.c_size_t)(), 2, 1, None) == 1
+    dst, src = (ctypes.c_void_p * 2)(4096, None), (ctypes.c_void_p * 2)(8192, 8192)
+    sizes = (ctypes.c_size_t * 2)(0, 64)              # the first block is empty and skipped, the second lacks a target
+    assert f(dst, src, sizes, 2, 0, None) == 1
+
+
 def test_dispatch_table():
     from matchattention_b200 import describe_dispatch
     assert describe_dispatch(8, 16, 1, torch.float16) == "fast cpl=2 lph=1"
