@@ -28,7 +28,7 @@ def bilinear_weights(max_offset: np.ndarray) -> np.ndarray:
     return np.stack([gx * gy, fx * gy, gx * fy, fx * fy], axis=-1).astype(dt)
 
 
-def forward(max_offset, q, k, v, H: int, W: int, r: int, scale: float):
+def forward(max_offset, q, k, v, H: int, W: int, r: int, scale: float, attn_type: str = "l1_norm"):
     """max_offset [B,Nq,h,2], q [B,Nq,C], k/v [B,H*W,C] -> (out [B,Nq,C], attn [B,Nq,h,M])."""
     dt = q.dtype
     assert dt in (np.float32, np.float16)
@@ -58,8 +58,11 @@ def forward(max_offset, q, k, v, H: int, W: int, r: int, scale: float):
             m = j * side + i
             tok[m] = ty * W + tx
             ktap = kh[bidx, tok[m], hidx]                       # [B,Nq,h,hd]
-            l1 = np.abs(qh - ktap).sum(axis=-1, dtype=np.float32).astype(dt)
-            score[..., m] = -l1
+            if attn_type == "dot_product":      # restated native-only scoring (parity unpinned): products rounded to dt
+                score[..., m] = (qh * ktap).astype(dt).sum(axis=-1, dtype=np.float32).astype(dt)
+            else:
+                l1 = np.abs(qh - ktap).sum(axis=-1, dtype=np.float32).astype(dt)
+                score[..., m] = -l1
     score = (score.astype(np.float32) * np.float32(scale)).astype(dt)
 
     # BilinearSoftmax (mat_pytorch_impl.py:78-165)

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import oracle
+from oracle import matchattn_numpy
 from _cases import assert_close, golden_names_with_prefix, load_golden
 
 
@@ -30,3 +31,13 @@ def test_scoring_functions_differ_and_unknown_is_refused():
     assert not torch.equal(l1, dot)
     with pytest.raises(KeyError):
         oracle.forward(*args, attn_type="l2_norm")
+
+
+@pytest.mark.parametrize("name", [n for n in golden_names_with_prefix("dot_") if not n.endswith("bf16")])
+def test_numpy_restatement_matches_the_restated_vectors(name):
+    """The second, independent restatement (numpy; no bfloat16 there)."""
+    c = load_golden(name)
+    out, attn = matchattn_numpy.forward(c["max_offset"].numpy(), c["q"].numpy(), c["k"].numpy(), c["v"].numpy(),
+                                        c["H"], c["W"], c["r"], c["scale"], attn_type="dot_product")
+    assert_close(torch.from_numpy(attn), c["attn"], c["dtype"], name + " attn")
+    assert_close(torch.from_numpy(out), c["out"], c["dtype"], name + " out")
